@@ -52,6 +52,7 @@ class PagedKV(CacheNeed):
     window: Optional[int] = None      # None: all keys are kept
     v_head_dim: Optional[int] = None  # None: as head_dim
     values_in_keys: bool = False      # True: a value is the leading v_head_dim elements of its key; no pages of its own
+    keep_first: int = 0               # with a window: positions below this stay visible, so their pages are never given back
 
     def group_key(self):
         return self
@@ -65,7 +66,8 @@ class PagedKV(CacheNeed):
                 (other.num_kv_heads, other.head_dim, other.v_head_dim or other.head_dim, other.values_in_keys):
             return None
         window = None if self.window is None or other.window is None else max(self.window, other.window)
-        return PagedKV(self.num_kv_heads, self.head_dim, window, self.v_head_dim, self.values_in_keys)
+        return PagedKV(self.num_kv_heads, self.head_dim, window, self.v_head_dim, self.values_in_keys,
+                       max(self.keep_first, other.keep_first))
 
     def make_group(self, cache_ids, num_pages: int, page_size: int, max_blocks: int) -> "CacheGroup":
         return CacheGroup(self, cache_ids, num_pages, page_size, max_blocks=max_blocks)
@@ -88,7 +90,8 @@ class PagedKV(CacheNeed):
 
     def most_pages_alone(self, total: int, chunk: int, page_size: int) -> int:
         span = total if self.window is None else min(total, self.window + chunk + page_size)
-        return (span + page_size - 1) // page_size
+        kept = (self.keep_first + page_size - 1) // page_size if self.window is not None else 0
+        return min((span + page_size - 1) // page_size + kept, (total + page_size - 1) // page_size)
 
 
 @dataclass(frozen=True)
@@ -108,6 +111,22 @@ class StateSlot(CacheNeed):
         return StateView(storage)
 
 
+@dataclass(frozen=True)
+class StateSlots(CacheNeed):
+    """Several per-request states of fixed shapes side by side (a mixer made of mixers, one that keeps a recurrence's state
+    and its last input): one tensor ``[slots, *shape]`` each."""
+    slots: Tuple[StateSlot, ...]
+
+    def make_storage(self, count: int, num_pages: int, page_size: int, num_slots: int, dtype, device):
+        if device is None:
+            return None
+        return [s.make_storage(count, num_pages, page_size, num_slots, dtype, device) for s in self.slots]
+
+    def make_view(self, storage, index: int, group_index: int, page_size: int):
+        from .manager import StateView, StateViews
+        return StateViews([StateView(None if storage is None else t) for t in (storage or [None] * len(self.slots))])
+
+
 class CacheGroup:
     """Host bookkeeping of one group: pool, block tables, trimming."""
 
@@ -117,7 +136,9 @@ class CacheGroup:
         self.cache_ids = list(cache_ids)
         self.page_size = page_size
         self.name = name or f"kv{need.num_kv_heads}x{need.head_dim}" + (f"v{need.v_head_dim}" if need.v_head_dim else "") + \
-            (f"w{need.window}" if need.window else "")
+            (f"w{need.window}" if need.window else "") + (f"k{need.keep_first}" if need.window and need.keep_first else "")
+        # blocks that hold positions which stay visible outside the window: never given back while the request lives
+        self.kept_blocks = (need.keep_first + page_size - 1) // page_size if need.window else 0
         self.pool = PagePool(num_pages, reserved=1, name=self.name)
         self.tables: Dict[object, List[int]] = {}      # request -> page of each block (NO_PAGE if none)
         self.first_block: Dict[object, int] = {}       # request -> first block still held
@@ -190,7 +211,7 @@ class CacheGroup:
         table = self.tables[req]
         keep_from = self._first_needed_block(new_len)
         freed = []
-        for b in range(self.first_block[req], min(keep_from, len(table))):
+        for b in range(max(self.first_block[req], self.kept_blocks), min(keep_from, len(table))):
             if table[b] != NO_PAGE:
                 freed.append(table[b])
                 table[b] = NO_PAGE

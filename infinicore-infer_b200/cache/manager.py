@@ -13,7 +13,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
-from .groups import NO_PAGE, CacheGroup, CacheNeed, PagedKV, StateSlot
+from .groups import NO_PAGE, CacheGroup, CacheNeed, PagedKV, StateSlot, StateSlots
 from .pages import OutOfPages
 from .slots import OutOfSlots, SlotAllocator
 
@@ -31,6 +31,19 @@ class StateView:
 
     def __init__(self, state):
         self.state = state
+
+
+class StateViews:
+    """The tensors of a ``StateSlots`` need, in its order."""
+
+    def __init__(self, views):
+        self.views = list(views)
+
+    def __getitem__(self, i: int) -> StateView:
+        return self.views[i]
+
+    def __len__(self) -> int:
+        return len(self.views)
 
 
 class CacheManager:
@@ -95,17 +108,23 @@ class CacheManager:
         for c, need in enumerate(needs):
             if need is not None and need.group_key() is None:
                 storage = need.make_storage(1, 0, page_size, self.slots.num_slots, dtype, device)
-                if storage is not None and hasattr(storage, "zero_"):
-                    self._state_tensors.append(storage)
+                self._keep_state(storage)
                 self.views[c] = need.make_view(storage, 0, -1, page_size)
 
         self.state_views: List[object] = [None] * len(entry_states)
         for i, need in enumerate(entry_states):
             if need is not None:
                 storage = need.make_storage(1, 0, page_size, self.slots.num_slots, dtype, device)
-                if storage is not None and hasattr(storage, "zero_"):
-                    self._state_tensors.append(storage)
+                self._keep_state(storage)
                 self.state_views[i] = need.make_view(storage, 0, -1, page_size)
+
+    def _keep_state(self, storage) -> None:
+        """Remember per-request state tensors (one, or a list of them): a slot is cleared when a request takes it."""
+        if storage is None:
+            return
+        for t in (storage if isinstance(storage, (list, tuple)) else [storage]):
+            if hasattr(t, "zero_"):
+                self._state_tensors.append(t)
 
     # ---- requests ------------------------------------------------------------------------
     def admit(self, req) -> int:

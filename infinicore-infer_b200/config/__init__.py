@@ -1,10 +1,11 @@
 """Configuration: typed specifications, the MiniCPM/FM9G config, the architecture registry."""
 from .specs import (AttentionSpec, BlockSpec, ConfigError, ConvAttentionSpec, FrequencyRampSpec, GLUSpec, LatentAttentionSpec,
-                    LayerNormSpec, LinearAttentionSpec, ModelSpec, PairRotarySpec, PostNormBlockSpec, ReinjectSpec, RMSNormSpec,
+                    LayerNormSpec, LinearAttentionSpec, MLPSpec, ModelSpec, PairRotarySpec, ParallelMixerSpec, PostNormBlockSpec, ReinjectSpec, RMSNormSpec,
                     RopeSpec, RoutedExpertsSpec, RunEntry, SandwichBlockSpec, SelectiveScanSpec, SwiGLUSpec, default_order)
 from .minicpm import MiniCPMConfig
 from .sitelorn import SitelornConfig
 from .vunelix import VunelixConfig
+from .vipovik import VipovikConfig
 from .presets import PRESETS, Preset
 from .registry import (architecture_names, config_class_for, read_config,
                        register_architecture)
@@ -15,8 +16,10 @@ for _name in ("minicpm", "fm9g", "llama", "MiniCPMForCausalLM", "LlamaForCausalL
 
 register_architecture("sitelorn", SitelornConfig)
 register_architecture("vunelix", VunelixConfig)
+register_architecture("vipovik", VipovikConfig)
 
 __all__ = [
+    "MLPSpec", "ParallelMixerSpec", "VipovikConfig",
     "FrequencyRampSpec", "LatentAttentionSpec", "ReinjectSpec", "RoutedExpertsSpec", "SandwichBlockSpec", "SelectiveScanSpec", "VunelixConfig",
     "ConvAttentionSpec", "GLUSpec", "LayerNormSpec", "LinearAttentionSpec", "PairRotarySpec", "PostNormBlockSpec", "SitelornConfig",
     "AttentionSpec", "BlockSpec", "ConfigError", "ModelSpec", "RMSNormSpec", "RopeSpec",

@@ -64,4 +64,24 @@ PRESETS: Dict[str, Preset] = {
             {"type": "mamba1", "mixer": {"inner": 64, "state": 20, "dt_rank": 4, "conv": 3},
              "mlp": {"kind": "moe", "router": {"experts": 4, "top": 1}, "expert": {"ff": 80}}},
         ]), 0.1, 0.05, 16),
+    # a small Vipovik: a span of two layers that runs twice, attention beside a recurrence in every layer, a dense and a
+    # routed feed-forward and a layer without one, a window with kept first tokens, partial rotation with and without stretching
+    "vipovik-tiny": Preset(dict(
+        architecture="Vipovik", vocab=320, width=96, embedding={"scale": 3.0}, norm={"eps": 1e-5}, loop={"start": 1, "stop": 3, "times": 2}, layers=[
+            {"type": "parallel", "mixer": {
+                "left": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 16, "scale": 0.3, "softcap": 15.0, "mask": {"size": 40, "keep_first": 3},
+                         "rot": {"base": 1e4, "dims": 16, "scaling": {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 1.0}}},
+                "right": {"heads": 3, "dim": 16, "rank": 8}, "left_scale": 0.7, "right_scale": 0.4},
+             "mlp": {"kind": "dense", "ff": 160}},
+            {"type": "parallel", "mixer": {
+                "left": {"heads": 2, "kv_heads": 1, "dim": 32, "vdim": 32, "scale": 0.25, "softcap": 30.0, "mask": {"size": 24, "keep_first": 1},
+                         "rot": {"base": 5e4, "dims": 32}},
+                "right": {"heads": 2, "dim": 24, "rank": 4}, "left_scale": 0.5, "right_scale": 0.6},
+             "mlp": {"kind": "moe", "router": {"experts": 6, "top": 2}, "expert": {"ff": 48, "limit": 1.5}}},
+            {"type": "parallel", "mixer": {
+                "left": {"heads": 3, "kv_heads": 3, "dim": 16, "vdim": 24, "scale": 0.35, "softcap": 10.0, "mask": {"size": 17, "keep_first": 5},
+                         "rot": {"base": 1e4, "dims": 8}},
+                "right": {"heads": 4, "dim": 8, "rank": 6}, "left_scale": 1.0, "right_scale": 1.0},
+             "mlp": None},
+        ]), 0.1, 0.05, 16),
 }

@@ -99,12 +99,14 @@ class FrequencyRampSpec:
 
 @dataclass(frozen=True)
 class PairRotarySpec:
-    """Rotation of the first ``dims`` elements of a head in pairs (2i, 2i+1) by the angle ``p * base ** (-2i / dims)``,
-    formed in float32 from the position; the other elements pass unchanged.  Needs no table and no longest position.
-    ``scaling`` stretches the frequencies (``FrequencyRampSpec``)."""
+    """Rotation of the first ``dims`` elements of a head in pairs by the angle ``p * base ** (-2i / dims)``, formed in
+    float32 from the position; the other elements pass unchanged.  ``layout`` "pairs": pair i is elements (2i, 2i+1);
+    "halves": elements (i, i + dims / 2).  Needs no table and no longest position.  ``scaling`` stretches the frequencies
+    (``FrequencyRampSpec``)."""
     dims: int
     base: float
     scaling: Optional[FrequencyRampSpec] = None
+    layout: str = "pairs"
     kind: str = "pair_rotary"
 
     def frequencies(self):
@@ -125,7 +127,9 @@ class ConvAttentionSpec:
     """Softmax attention over a paged cache with grouped heads whose keys and values may differ in size, and with these
     options, each a parameter: a short causal convolution over time on every channel of the q, k and v projections
     (``conv_taps`` taps, 0 for none), an RMS norm over the WHOLE q and the whole k projection (``qk_norm``), a rotation
-    (``position``), a sliding window, a sink (a key of score 0 without a value in every softmax), one output gate per
+    (``position``), after it a division of every head of q and k by its root mean square (``head_norm``, eps
+    ``qk_norm_eps``), a cap on the scores (``score_cap`` c > 0: s <- c tanh(s / c)), a sliding window that may keep the
+    first ``keep_first`` positions visible for good, a sink (a key of score 0 without a value in every softmax), one output gate per
     head (sigmoid of a projection of the mixer's input), and ``shares_kv``: the layer makes queries only and reads the
     keys and values that another layer wrote into its cache.  The names are those of the checkpoint's tensors below the
     mixer's prefix: projection ``q``, its convolution ``q`` + ``conv_suffix``, its norm ``q`` + ``norm_suffix``."""
@@ -143,6 +147,9 @@ class ConvAttentionSpec:
     sink: bool = False
     head_gate: bool = False
     shares_kv: bool = False
+    head_norm: bool = False
+    score_cap: float = 0.0
+    keep_first: int = 0
     q_name: str = "q"
     k_name: str = "k"
     v_name: str = "v"
@@ -163,7 +170,15 @@ class LinearAttentionSpec:
     [rank, hidden]; W2: ``decay_up_name`` [heads * head_dim, rank] with bias ``decay_up_name`` + ``bias_suffix``).
     ``qkv_act`` acts on q, k and v ("none" or "silu"); q is multiplied by ``q_scale``.  The output passes an RMS norm,
     over all heads at once with a weight of heads * v_head_dim (``norm_per_head`` False) or per head with one weight of
-    v_head_dim shared by the heads, is multiplied by ``gate_act`` of a projection of the mixer's input, and projected."""
+    v_head_dim shared by the heads, is multiplied by ``gate_act`` of a projection of the mixer's input, and projected.
+
+    Options that another recurrence of this family takes: ``token_shift``: each of q, k, v, the gate and the decay's
+    projection reads its own mixture h_t + (h_(t-1) - h_t) * mu of a row and the row before it (mu: ``shift_prefix`` + the
+    projection's name; the decay's is ``shift_prefix`` + ``decay_shift_name``), the last row being part of the request's
+    state; ``bonus_name``: a tensor u [heads, head_dim], and a row reads the state BEFORE its own decay with a bonus for its
+    own key, o_t = (S_(t-1) + diag(u) k_t v_t^T)^T q_t; ``decay_form`` "exp_neg_exp": a_t = exp(-exp(z)) instead of
+    sigmoid(z) ** (1 / tau); ``decay_act``: an activation on W1's output; ``decay_bias_name`` names the bias of W2;
+    ``norm_per_head`` "unit": the mean per head, a weight of heads * v_head_dim."""
     hidden_size: int
     num_heads: int
     head_dim: int
@@ -185,6 +200,13 @@ class LinearAttentionSpec:
     decay_down_name: str = "a1"
     decay_up_name: str = "a2"
     bias_suffix: str = ".b"
+    token_shift: bool = False
+    shift_prefix: str = "mu."
+    decay_shift_name: str = "w"
+    bonus_name: Optional[str] = None
+    decay_form: str = "sigmoid_pow"
+    decay_act: str = "none"
+    decay_bias_name: Optional[str] = None
     kind: str = "linear_attention"
 
 
@@ -245,7 +267,11 @@ class SelectiveScanSpec:
 class RoutedExpertsSpec:
     """A feed-forward of ``num_experts`` small gated units of which each row uses ``top``: scores are sigmoid(router h) in
     float32; the ``top`` largest choose the experts; an expert sees score * h (``scale_input``) and the outputs add up
-    without renormalising.  ``shared``: a gated unit that every row passes, added on top."""
+    without renormalising.  ``shared``: a gated unit that every row passes, added on top.
+
+    ``score_form`` "softmax_renorm": scores are softmax(router h) over all experts, the chosen ones' scores are divided by
+    their sum (+ 1e-20) and multiply the units' OUTPUTS (``scale_input`` False).  ``act`` "swish_clamp": a unit's inner value
+    is g' sigmoid(1.702 g') (u' + 1) with g' = min(gate h, limit), u' = clamp(up h, -limit, limit)."""
     hidden_size: int
     num_experts: int
     top: int
@@ -253,6 +279,8 @@ class RoutedExpertsSpec:
     act: str = "silu"
     shared: Optional[object] = None
     scale_input: bool = True
+    score_form: str = "sigmoid"
+    limit: float = 0.0
     router_name: str = "router"
     expert_prefix: str = "e{}."
     shared_prefix: str = "shared."
@@ -306,6 +334,31 @@ class GLUSpec:
 
 
 @dataclass(frozen=True)
+class MLPSpec:
+    """down(act(up(x))): a feed-forward without a gate; ``act`` "gelu_erf" (0.5 z (1 + erf(z / sqrt 2))), "gelu_tanh", "silu" or
+    "relu"."""
+    hidden_size: int
+    intermediate_size: int
+    act: str = "gelu_erf"
+    up_name: str = "up"
+    down_name: str = "down"
+    kind: str = "mlp"
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Two mixers side by side that read the same input: ``left_scale`` * left(h) + ``right_scale`` * right(h).  Each is any
+    mixer's specification; at most one of them keeps pages."""
+    left: object
+    right: object
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    left_prefix: str = "left."
+    right_prefix: str = "right."
+    kind: str = "parallel"
+
+
+@dataclass(frozen=True)
 class PostNormBlockSpec:
     """One layer whose norms sit on the sublayers' outputs: x += norm_a(mixer(x)); x += norm_b(feed_forward(x)).  The
     sublayers read the stream itself.  ``feed_forward`` None: the layer has a mixer only."""
@@ -322,15 +375,16 @@ class PostNormBlockSpec:
 
 @dataclass(frozen=True)
 class BlockSpec:
-    """One layer: x += s * mixer(norm_a(x)); x += s * feed_forward(norm_b(x)).
+    """One layer: x += s * mixer(norm_a(x)); x += s * feed_forward(norm_b(x)).  ``feed_forward`` None: the layer has a
+    mixer only.
 
     The four ``*_prefix`` strings are the names, below the layer's own prefix,
     under which the checkpoint stores each part's tensors.
     """
     mixer: object
-    feed_forward: object
+    feed_forward: Optional[object]
     mixer_norm: object
-    ffn_norm: object
+    ffn_norm: Optional[object]
     residual_scale: float = 1.0
     mixer_prefix: str = "self_attn."
     ffn_prefix: str = "mlp."

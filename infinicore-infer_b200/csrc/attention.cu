@@ -34,6 +34,10 @@ struct AttnArgs {
     int dv, sink;
     const float *gate;
     int gate_ld;
+    // a cap on the scores, s <- cap tanh(s / cap) (0: none), and keys at positions below `keep_first` that stay visible
+    // when the window has passed them
+    float cap;
+    int keep_first;
 };
 
 // ---------------------------------------------------------------------------------------
@@ -76,9 +80,13 @@ attention_row_kernel(AttnArgs a) {
 #pragma unroll
     for (int i = 0; i < NS; ++i) acc[i] = 0.f;
 
-    for (int j0 = lo; j0 <= pos; j0 += 32) {
+    // two ranges of keys: the kept first ones that the window has passed, then the window
+    const int kept = min(a.keep_first, lo);
+    for (int range = kept > 0 ? 0 : 1; range < 2; ++range) {
+    const int begin = range == 0 ? 0 : lo, end = range == 0 ? kept - 1 : pos;
+    for (int j0 = begin; j0 <= end; j0 += 32) {
         const int j = j0 + lane;
-        const bool valid = j <= pos;
+        const bool valid = j <= end;
         size_t row_off = 0;
         float s = -INFINITY;
         if (valid) {
@@ -88,6 +96,7 @@ attention_row_kernel(AttnArgs a) {
             float dot = 0.f;
             for (int e = 0; e < dh; ++e) dot = fmaf(qs[e], to_f32(kr[e]), dot);
             s = dot * a.scale;
+            if (a.cap > 0.f) s = a.cap * tanhf(s / a.cap);
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -96,7 +105,7 @@ attention_row_kernel(AttnArgs a) {
         m = m_new;
 #pragma unroll
         for (int i = 0; i < NS; ++i) acc[i] *= corr;
-        const int n = min(32, pos - j0 + 1);
+        const int n = min(32, end - j0 + 1);
         for (int jj = 0; jj < n; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const unsigned long long off = __shfl_sync(0xffffffffu, (unsigned long long)row_off, jj);
@@ -107,6 +116,7 @@ attention_row_kernel(AttnArgs a) {
                 if (e < dv) acc[i] = fmaf(pj, to_f32(vr[e]), acc[i]);
             }
         }
+    }
     }
     if (a.sink) {       // one more key of score 0 that brings no value
         const float m_new = fmaxf(m, 0.f);
@@ -138,11 +148,11 @@ JK_EXPORT int jk_attention_rows(const void *q, const void *k_pages, const void *
                                 int dtype, const int *positions, const int *row_req,
                                 const int *block_table, int max_blocks, int page_size, int T, int nh,
                                 int nkvh, int dh, float scale, int window, int dv, int sink, const float *gate, int gate_ld,
-                                cudaStream_t stream) {
+                                float cap, int keep_first, cudaStream_t stream) {
     if (T == 0) return JK_OK;
     if (dv <= 0) dv = dh;
     AttnArgs a{q, k_pages, v_pages, out, positions, row_req, block_table,
-               T, nh, nkvh, dh, page_size, max_blocks, window, scale, dv, sink, gate, gate_ld};
+               T, nh, nkvh, dh, page_size, max_blocks, window, scale, dv, sink, gate, gate_ld, cap, window > 0 ? keep_first : 0};
     if (int rc = check_args(a)) return rc;
     JK_REQUIRE(dh <= ROW_MAX_DH && dv <= ROW_MAX_DH, "attention: head size %d / %d exceeds %d", dh, dv, ROW_MAX_DH);
     JK_REQUIRE(gate == nullptr || gate_ld >= nh, "attention: a gate row of %d holds no %d heads", gate_ld, nh);

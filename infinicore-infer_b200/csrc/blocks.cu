@@ -30,7 +30,7 @@ __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-enum BlockAct : int { BACT_NONE = 0, BACT_SILU = 1, BACT_GELU_TANH = 2, BACT_SIGMOID = 3, BACT_RELU = 4 };
+enum BlockAct : int { BACT_NONE = 0, BACT_SILU = 1, BACT_GELU_TANH = 2, BACT_SIGMOID = 3, BACT_RELU = 4, BACT_SWISH_CLAMP = 6 };
 __device__ __forceinline__ float block_act(int act, float z) {
     switch (act) {
         case BACT_SILU: return silu_f(z);
@@ -39,6 +39,18 @@ __device__ __forceinline__ float block_act(int act, float z) {
         case BACT_RELU: return fmaxf(z, 0.f);
         default: return z;
     }
+}
+
+// A gated unit's inner value from its two sums g and u and the score s of the row's choice (1 where the score multiplies the
+// unit's output instead): act(s g) (s u), or, for BACT_SWISH_CLAMP, with g' = min(g, limit) and u' = clamp(u, -limit, limit),
+// g' sigmoid(1.702 g') (u' + 1).
+__device__ __forceinline__ float expert_inner(int act, float s, float g, float u, float limit) {
+    if (act == BACT_SWISH_CLAMP) {
+        g = fminf(s * g, limit);
+        u = fminf(fmaxf(s * u, -limit), limit);
+        return g * sigmoid_f(1.702f * g) * (u + 1.f);
+    }
+    return block_act(act, s * g) * (s * u);
 }
 
 #define BLOCKS_BY_DTYPE(dtype, name, LAUNCH)                                      \
@@ -1299,7 +1311,7 @@ JK_EXPORT int jk_selective_scan(const float *x, const float *low, int ld_low, in
 // ---------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void route_topk_kernel(const T *__restrict__ h, const float *__restrict__ router, int D, int E, int top, int *__restrict__ ids,
-                                  float *__restrict__ scores, int *__restrict__ counts) {
+                                  float *__restrict__ scores, int *__restrict__ counts, int score_form) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float z[];        // [E]
@@ -1327,16 +1339,27 @@ __global__ void route_topk_kernel(const T *__restrict__ h, const float *__restri
     }
     __syncthreads();
     if (threadIdx.x == 0) {
+        // score_form 1: softmax over all experts; the chosen ones' scores divided by their sum
+        float zmax = -INFINITY, total = 1.f, chosen = 0.f;
+        if (score_form == 1) {
+            for (int e = 0; e < E; ++e) zmax = fmaxf(zmax, z[e]);
+            total = 0.f;
+            for (int e = 0; e < E; ++e) total += expf(z[e] - zmax);
+        }
         for (int k = 0; k < top; ++k) {
             int best = -1;
             float bz = -INFINITY;
             for (int e = 0; e < E; ++e)
                 if (best < 0 || z[e] > bz) { bz = z[e]; best = e; }
             ids[(size_t)t * top + k] = best;
-            scores[(size_t)t * top + k] = sigmoid_f(bz);
+            const float sc = score_form == 1 ? expf(bz - zmax) / total : sigmoid_f(bz);
+            scores[(size_t)t * top + k] = sc;
+            chosen += sc;
             atomicAdd(&counts[best], 1);
             z[best] = -INFINITY;
         }
+        if (score_form == 1)
+            for (int k = 0; k < top; ++k) scores[(size_t)t * top + k] /= chosen + 1e-20f;
     }
 }
 
@@ -1395,7 +1418,7 @@ __device__ __forceinline__ bool expert_tile(const int *starts, int E, int block,
 template <typename T>
 __global__ void __launch_bounds__(256) expert_gate_up_kernel(const T *__restrict__ h, const T *__restrict__ w, T *__restrict__ act, int D, int ff, int E,
                                                              const int *__restrict__ starts, const int *__restrict__ entry_row,
-                                                             const float *__restrict__ entry_score, int actf) {
+                                                             const float *__restrict__ entry_score, int actf, float limit) {
     pdl_trigger();
     pdl_wait();
     int e, m0;
@@ -1411,8 +1434,8 @@ __global__ void __launch_bounds__(256) expert_gate_up_kernel(const T *__restrict
         r += m0;
         const int n = n0 + c;
         if (r >= M || n >= ff) continue;
-        const float s = entry_score[first + r];
-        act[(size_t)(first + r) * ff + n] = from_f32<T>(block_act(actf, s * g[e]) * (s * u[e]));
+        const float s = entry_score ? entry_score[first + r] : 1.f;
+        act[(size_t)(first + r) * ff + n] = from_f32<T>(expert_inner(actf, s, g[e], u[e], limit));
     }
 }
 
@@ -1462,7 +1485,7 @@ __device__ __forceinline__ void unpack16(const uint4 &v, float *f) {
 // the features of one block against ROWS staged entries (the caller picks the smallest ROWS that holds them)
 template <typename T, bool GLU, int ROWS>
 __device__ __forceinline__ void expert_rows_features(const T *__restrict__ er_rows, const T *__restrict__ we, void *__restrict__ out, int K, int N,
-                                                     int rows, size_t entry0, const float *__restrict__ entry_score, int actf) {
+                                                     int rows, size_t entry0, const float *__restrict__ entry_score, int actf, float limit) {
     constexpr int V = Vec16<T>::N;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int f = warp; f < ER_FEATURES; f += 8) {
@@ -1499,8 +1522,8 @@ __device__ __forceinline__ void expert_rows_features(const T *__restrict__ er_ro
                 if (r >= rows) break;
                 const size_t entry = entry0 + r;
                 if (GLU) {
-                    const float sc = entry_score[entry];
-                    ((T *)out)[entry * N + n] = from_f32<T>(block_act(actf, sc * g[r]) * (sc * u[r]));
+                    const float sc = entry_score ? entry_score[entry] : 1.f;
+                    ((T *)out)[entry * N + n] = from_f32<T>(expert_inner(actf, sc, g[r], u[r], limit));
                 } else {
                     ((float *)out)[entry * N + n] = g[r];
                 }
@@ -1513,7 +1536,7 @@ __device__ __forceinline__ void expert_rows_features(const T *__restrict__ er_ro
 template <typename T, bool GLU>
 __global__ void __launch_bounds__(256) expert_rows_kernel(const T *__restrict__ in, const T *__restrict__ w, void *__restrict__ out, int K, int N, int E,
                                                           const int *__restrict__ starts, const int *__restrict__ entry_row,
-                                                          const float *__restrict__ entry_score, int actf) {
+                                                          const float *__restrict__ entry_score, int actf, float limit) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char er_smem[];
@@ -1534,23 +1557,27 @@ __global__ void __launch_bounds__(256) expert_rows_kernel(const T *__restrict__ 
         }
         __syncthreads();
         const size_t entry0 = (size_t)(first + r0);
-        if (rows <= 1) expert_rows_features<T, GLU, 1>(er_rows, we, out, K, N, rows, entry0, entry_score, actf);
-        else if (rows <= 2) expert_rows_features<T, GLU, 2>(er_rows, we, out, K, N, rows, entry0, entry_score, actf);
-        else if (rows <= 4) expert_rows_features<T, GLU, 4>(er_rows, we, out, K, N, rows, entry0, entry_score, actf);
-        else expert_rows_features<T, GLU, 8>(er_rows, we, out, K, N, rows, entry0, entry_score, actf);
+        if (rows <= 1) expert_rows_features<T, GLU, 1>(er_rows, we, out, K, N, rows, entry0, entry_score, actf, limit);
+        else if (rows <= 2) expert_rows_features<T, GLU, 2>(er_rows, we, out, K, N, rows, entry0, entry_score, actf, limit);
+        else if (rows <= 4) expert_rows_features<T, GLU, 4>(er_rows, we, out, K, N, rows, entry0, entry_score, actf, limit);
+        else expert_rows_features<T, GLU, 8>(er_rows, we, out, K, N, rows, entry0, entry_score, actf, limit);
     }
 }
 
-// delta[t] (+)= sum over the row's choices, in their order, of y[pair_entry[t * top + k]]
+// delta[t] (+)= sum over the row's choices, in their order, of y[pair_entry[t * top + k]] (times the choice's score where
+// `entry_score` is given: the form in which the score multiplies a unit's output)
 __global__ void expert_combine_kernel(const float *__restrict__ y, const int *__restrict__ pair_entry, float *__restrict__ delta, int D, int top,
-                                      int add, size_t total) {
+                                      int add, size_t total, const float *__restrict__ entry_score) {
     pdl_trigger();
     pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / D;
         const int c = (int)(i % D);
         float v = add ? delta[i] : 0.f;
-        for (int k = 0; k < top; ++k) v += y[(size_t)pair_entry[t * top + k] * D + c];
+        for (int k = 0; k < top; ++k) {
+            const int entry = pair_entry[t * top + k];
+            v = entry_score ? fmaf(entry_score[entry], y[(size_t)entry * D + c], v) : v + y[(size_t)entry * D + c];
+        }
         delta[i] = v;
     }
 }
@@ -1563,7 +1590,7 @@ JK_EXPORT long long jk_routed_experts_workspace(int T, int E, int top) { return 
 // [T top, ff] of the activation type, `y` [T top, D] float32.
 JK_EXPORT int jk_routed_experts(const void *h, const float *router, const void *w_gate_up, const void *w_down, float *delta, int add,
                                 int dtype, int T, int D, int ff, int E, int top, int actf, int *route, void *act, float *y,
-                                cudaStream_t stream) {
+                                int score_form, float limit, cudaStream_t stream) {
     if (T == 0) return JK_OK;
     JK_REQUIRE(h && router && w_gate_up && w_down && delta && route && act && y, "routed_experts: an argument is missing");
     JK_REQUIRE(D > 0 && ff > 0 && E > 0 && top > 0 && top <= E, "routed_experts: %d experts, %d a row, sizes %d and %d", E, top, D, ff);
@@ -1572,7 +1599,7 @@ JK_EXPORT int jk_routed_experts(const void *h, const float *router, const void *
     int *counts = route, *starts = counts + E, *ids = starts + E + 1, *entry_row = ids + pairs, *pair_entry = entry_row + pairs;
     float *scores = (float *)(pair_entry + pairs), *entry_score = scores + pairs;
     if (cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)E, stream) != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "routed_experts: clearing the counts failed");
-#define LAUNCH(TT) jk_launch(route_topk_kernel<TT>, dim3(T), dim3(128), (size_t)E * sizeof(float), stream, (const TT *)h, router, D, E, top, ids, scores, counts)
+#define LAUNCH(TT) jk_launch(route_topk_kernel<TT>, dim3(T), dim3(128), (size_t)E * sizeof(float), stream, (const TT *)h, router, D, E, top, ids, scores, counts, score_form)
     BLOCKS_BY_DTYPE(dtype, "route_topk", LAUNCH);
 #undef LAUNCH
     JK_CHECK_LAUNCH("route_topk");
@@ -1580,6 +1607,8 @@ JK_EXPORT int jk_routed_experts(const void *h, const float *router, const void *
               starts, entry_row, entry_score, pair_entry);
     JK_CHECK_LAUNCH("route_sort");
     // few rows: the experts' matrices stream past their entries (rows of 16-byte multiples); else tiles
+    // score_form 1: the score multiplies the unit's output (in the sum of a row's choices), not its input
+    const float *in_score = score_form == 1 ? nullptr : entry_score, *out_score = score_form == 1 ? entry_score : nullptr;
     const int per16 = dtype == JK_F32 ? 4 : 8;
     const bool stream_rows = pairs <= 64 && D % per16 == 0 && ff % per16 == 0 && (uintptr_t)w_gate_up % 16 == 0 && (uintptr_t)w_down % 16 == 0 &&
                              (size_t)ER_ROWS * std::max(D, ff) * 4 <= 160 * 1024;
@@ -1589,9 +1618,9 @@ JK_EXPORT int jk_routed_experts(const void *h, const float *router, const void *
     if (smem_up > 48 * 1024) cudaFuncSetAttribute(expert_rows_kernel<TT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);  \
     if (smem_down > 48 * 1024) cudaFuncSetAttribute(expert_rows_kernel<TT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down); \
     jk_launch(expert_rows_kernel<TT, true>, dim3(E, (ff + ER_FEATURES - 1) / ER_FEATURES), dim3(256), smem_up, stream, (const TT *)h,        \
-              (const TT *)w_gate_up, act, D, ff, E, (const int *)starts, (const int *)entry_row, (const float *)entry_score, actf);          \
+              (const TT *)w_gate_up, act, D, ff, E, (const int *)starts, (const int *)entry_row, in_score, actf, limit);          \
     jk_launch(expert_rows_kernel<TT, false>, dim3(E, (D + ER_FEATURES - 1) / ER_FEATURES), dim3(256), smem_down, stream, (const TT *)act,    \
-              (const TT *)w_down, (void *)y, ff, D, E, (const int *)starts, (const int *)nullptr, (const float *)nullptr, 0)
+              (const TT *)w_down, (void *)y, ff, D, E, (const int *)starts, (const int *)nullptr, (const float *)nullptr, 0, 0.f)
         BLOCKS_BY_DTYPE(dtype, "expert rows", LAUNCH);
 #undef LAUNCH
         JK_CHECK_LAUNCH("expert rows");
@@ -1599,7 +1628,7 @@ JK_EXPORT int jk_routed_experts(const void *h, const float *router, const void *
     const int tiles = (pairs + GT_M - 1) / GT_M + E;
 #define LAUNCH(TT)                                                                                                                          \
     jk_launch(expert_gate_up_kernel<TT>, dim3(tiles, (ff + GT_N - 1) / GT_N), dim3(256), 0, stream, (const TT *)h, (const TT *)w_gate_up,  \
-              (TT *)act, D, ff, E, (const int *)starts, (const int *)entry_row, (const float *)entry_score, actf);                          \
+              (TT *)act, D, ff, E, (const int *)starts, (const int *)entry_row, in_score, actf, limit);                          \
     jk_launch(expert_down_kernel<TT>, dim3(tiles, (D + GT_N - 1) / GT_N), dim3(256), 0, stream, (const TT *)act, (const TT *)w_down, y, D, \
               ff, E, (const int *)starts)
     BLOCKS_BY_DTYPE(dtype, "expert products", LAUNCH);
@@ -1608,7 +1637,7 @@ JK_EXPORT int jk_routed_experts(const void *h, const float *router, const void *
     }
     const size_t total = (size_t)T * D;
     jk_launch(expert_combine_kernel, dim3((int)std::min<size_t>((total + 255) / 256, 148 * 16)), dim3(256), 0, stream, (const float *)y,
-              (const int *)pair_entry, delta, D, top, add, total);
+              (const int *)pair_entry, delta, D, top, add, total, out_score);
     JK_CHECK_LAUNCH("expert_combine");
     return JK_OK;
 }

@@ -27,13 +27,15 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 // log(sigmoid(z)) without overflow on either side
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
-enum MixAct : int { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_TANH = 2, ACT_SIGMOID = 3, ACT_RELU = 4 };
+enum MixAct : int { ACT_NONE = 0, ACT_SILU = 1, ACT_GELU_TANH = 2, ACT_SIGMOID = 3, ACT_RELU = 4, ACT_GELU_ERF = 5, ACT_TANH = 7 };
 __device__ __forceinline__ float apply_act(int act, float z) {
     switch (act) {
         case ACT_SILU: return silu_f(z);
         case ACT_GELU_TANH: return gelu_tanh_f(z);
         case ACT_SIGMOID: return sigmoid_f(z);
         case ACT_RELU: return fmaxf(z, 0.f);
+        case ACT_GELU_ERF: return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
+        case ACT_TANH: return tanhf(z);
         default: return z;
     }
 }
@@ -218,6 +220,9 @@ struct ConvQkvArgs {
     float *tail;                // [slots, taps - 1, nq + nk + nv]
     int taps, dk, dv, kv_heads, rot_dims;
     float eps;
+    int rot_half;               // 1: element i < rot_dims / 2 of a head pairs with element i + rot_dims / 2 (else 2i with 2i + 1)
+    float rot_mag;              // factor of cos and sin
+    int head_norm;              // 1: after the rotation every head of q and k is divided by its root mean square (eps inside)
     const int *positions, *row_req, *req_start, *slot_ids, *block_table;
     int max_blocks, page_size;
     void *q_out, *k_pages, *v_pages;
@@ -279,18 +284,61 @@ __global__ void conv_qkv_kernel(ConvQkvArgs a) {
         const size_t row = (size_t)page * a.kv_heads * a.page_size + (size_t)(pos % a.page_size);
         k_row = row; v_row = row;
     }
+    if (a.head_norm) {
+        // a warp per head of q and k: rotate, the head's sum of squares, divide, store
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+        const int half = a.rot_dims >> 1, heads = (a.nq + a.nk) / a.dk;
+        for (int hh = warp; hh < heads; hh += nwarp) {
+            const float *yh = y + (size_t)hh * a.dk;
+            float ss = 0.f;
+            for (int e = lane; e < a.dk; e += 32) {
+                float val = yh[e];
+                if (e < a.rot_dims) {
+                    const bool first = a.rot_half ? e < half : !(e & 1);
+                    const int pair = a.rot_half ? (first ? e : e - half) : e >> 1;
+                    const float other = yh[a.rot_half ? (first ? e + half : e - half) : (first ? e + 1 : e - 1)];
+                    float sn, cs;
+                    sincosf(fpos * a.freq[pair], &sn, &cs);
+                    sn *= a.rot_mag; cs *= a.rot_mag;
+                    val = first ? val * cs - other * sn : val * cs + other * sn;
+                }
+                ss += val * val;
+            }
+            const float inv = 1.f / sqrtf(warp_sum(ss) / (float)a.dk + a.eps);
+            for (int e = lane; e < a.dk; e += 32) {
+                float val = yh[e];
+                if (e < a.rot_dims) {
+                    const bool first = a.rot_half ? e < half : !(e & 1);
+                    const int pair = a.rot_half ? (first ? e : e - half) : e >> 1;
+                    const float other = yh[a.rot_half ? (first ? e + half : e - half) : (first ? e + 1 : e - 1)];
+                    float sn, cs;
+                    sincosf(fpos * a.freq[pair], &sn, &cs);
+                    sn *= a.rot_mag; cs *= a.rot_mag;
+                    val = first ? val * cs - other * sn : val * cs + other * sn;
+                }
+                const int c = hh * a.dk + e;
+                if (c < a.nq) q_out[c] = from_f32<T>(val * inv);
+                else ((T *)a.k_pages)[(k_row + (size_t)((c - a.nq) / a.dk) * a.page_size) * a.dk + e] = from_f32<T>(val * inv);
+            }
+        }
+    }
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
         if (c < a.nq + a.nk) {
+            if (a.head_norm) continue;
             const bool is_q = c < a.nq;
             const int cc = is_q ? c : c - a.nq;
             const int head = cc / a.dk, e = cc % a.dk;
             float val = y[c];
             if (e < a.rot_dims) {
-                const float ang = fpos * a.freq[e >> 1];
+                const int half = a.rot_dims >> 1;
+                const bool first = a.rot_half ? e < half : !(e & 1);
+                const int pair = a.rot_half ? (first ? e : e - half) : e >> 1;
+                const float ang = fpos * a.freq[pair];
                 float sn, cs;
                 sincosf(ang, &sn, &cs);
-                const float other = y[(e & 1) ? c - 1 : c + 1];
-                val = (e & 1) ? fmaf(val, cs, other * sn) : fmaf(val, cs, -other * sn);
+                sn *= a.rot_mag; cs *= a.rot_mag;
+                const float other = y[a.rot_half ? (first ? c + half : c - half) : (first ? c + 1 : c - 1)];
+                val = first ? fmaf(val, cs, -other * sn) : fmaf(val, cs, other * sn);
             }
             if (is_q) q_out[cc] = from_f32<T>(val);
             else ((T *)a.k_pages)[(k_row + (size_t)head * a.page_size) * a.dk + e] = from_f32<T>(val);
@@ -330,13 +378,14 @@ JK_EXPORT int jk_conv_qkv(const float *u, int ld, int q_off, int k_off, int v_of
                           const float *norm_q, const float *norm_k, float eps, const float *freq, int rot_dims, float *tail,
                           const int *positions, const int *row_req, const int *req_start, const int *slot_ids,
                           const int *block_table, int max_blocks, int page_size, void *q_out, void *k_pages, void *v_pages,
-                          int dtype, int T, int nreq, cudaStream_t stream) {
+                          int dtype, int T, int nreq, int rot_half, float rot_mag, int head_norm, cudaStream_t stream) {
     if (T == 0) return JK_OK;
     ConvQkvArgs a;
     a.u = u; a.ld = ld; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off;
     a.nq = heads * dk; a.nk = has_kv ? kv_heads * dk : 0; a.nv = has_kv ? kv_heads * dv : 0;
     a.conv_q = conv_q; a.conv_k = conv_k; a.conv_v = conv_v; a.norm_q = norm_q; a.norm_k = norm_k; a.freq = freq; a.tail = tail;
     a.taps = taps; a.dk = dk; a.dv = dv; a.kv_heads = kv_heads; a.rot_dims = rot_dims; a.eps = eps;
+    a.rot_half = rot_half; a.rot_mag = rot_mag > 0.f ? rot_mag : 1.f; a.head_norm = head_norm;
     a.positions = positions; a.row_req = row_req; a.req_start = req_start; a.slot_ids = slot_ids; a.block_table = block_table;
     a.max_blocks = max_blocks; a.page_size = page_size; a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages;
     const bool conv = conv_q || conv_k || conv_v;
@@ -417,6 +466,13 @@ struct ScanArgs {
     int vec4;                   // 1: rows, offsets and sizes are multiples of four floats: staging moves 16 bytes at a time
     int dkp;                    // channels of a staged row: dk rounded up to kq * KS; the padding stays zero, so the scan's
                                 // inner loop needs no bounds
+    // The form in which a row reads the state BEFORE its own decay, with a bonus for its own key:
+    //     o_t = (S_(t-1) + diag(bonus) k_t v_t^T)^T q_t,  then  S_t = diag(a_t) S_(t-1) + k_t v_t^T
+    // (bonus [heads, dk]; null: the form above, o_t = S_t^T q_t).  The running product that the prefix kernel multiplies a
+    // row's query by is then the one up to the row BEFORE it.
+    const float *bonus;
+    int decay_form;             // projected decay: 0 sigmoid(z)^(1/tau), 1 exp(-exp(z))
+    int rank_act;               // MixAct on the decay projection's `rank` columns before W2
 };
 
 constexpr int SCAN_THREADS = 256;     // (column pair, part) threads: a row staged once serves 128 columns at four lanes a column
@@ -458,6 +514,7 @@ linear_scan_kernel(ScanArgs a) {
 #pragma unroll
         for (int i = 0; i < KS; ++i) s[c][i] = (!piece && live[c] && part + i * kq < dk) ? S[(size_t)(part + i * kq) * a.dv + c] : 0.f;
     const float head_decay = a.decay ? a.decay[head] : 1.f;
+    const bool with_bonus = a.bonus != nullptr;
     const bool write_cum = piece && a.w2 != nullptr && blockIdx.z == 0;
     if (dkp > dk)       // the padding channels: zero once, nothing writes them afterwards
         for (int i = threadIdx.x; i < a.chunk * dkp; i += SCAN_THREADS) sx[i] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -467,7 +524,7 @@ linear_scan_kernel(ScanArgs a) {
         if (a.w2 != nullptr)
             for (int i = threadIdx.x; i < n * a.rank; i += SCAN_THREADS) {
                 const int tt = i / a.rank;
-                sr[i] = a.u[(size_t)(t0 + tt) * a.ld + a.r_off + (i - tt * a.rank)];
+                sr[i] = apply_act(a.rank_act, a.u[(size_t)(t0 + tt) * a.ld + a.r_off + (i - tt * a.rank)]);
             }
         if (a.vec4) {
             // four neighbouring channels of a row at a time, all of a thread's loads ahead of the arithmetic
@@ -494,6 +551,7 @@ linear_scan_kernel(ScanArgs a) {
                             sx[at + e].y = apply_act(a.qkv_act, kk4[e]);
                             sx[at + e].z = apply_act(a.qkv_act, qq[e]) * a.q_scale;
                             if (a.w2 == nullptr) sx[at + e].x = head_decay;
+                            if (a.bonus != nullptr) sx[at + e].w = a.bonus[head * dk + i % dk + e];
                         }
                     }
                 }
@@ -520,6 +578,7 @@ linear_scan_kernel(ScanArgs a) {
                         sx[at].y = apply_act(a.qkv_act, kv[j]);
                         sx[at].z = apply_act(a.qkv_act, qv[j]) * a.q_scale;
                         if (a.w2 == nullptr) sx[at].x = head_decay;
+                        if (a.bonus != nullptr) sx[at].w = a.bonus[head * dk + i % dk];
                     }
                 }
             }
@@ -535,7 +594,7 @@ linear_scan_kernel(ScanArgs a) {
                 const TW *w = (const TW *)a.w2 + (size_t)(head * dk + kk) * a.rank;
                 float z = a.b2 ? a.b2[head * dk + kk] : 0.f;
                 for (int r = 0; r < a.rank; ++r) z = fmaf(to_f32(w[r]), sr[tt * a.rank + r], z);
-                sx[tt * dkp + kk].x = expf(log_sigmoid_f(z) * a.inv_tau);
+                sx[tt * dkp + kk].x = a.decay_form == 1 ? expf(-expf(z)) : expf(log_sigmoid_f(z) * a.inv_tau);
             }
             __syncthreads();
         }
@@ -558,8 +617,14 @@ linear_scan_kernel(ScanArgs a) {
                 const float4 e = x[i * kq];
 #pragma unroll
                 for (int c = 0; c < SCAN_CPT; ++c) {
-                    s[c][i] = fmaf(e.x, s[c][i], e.y * vv[c]);
-                    o[c][i & 1] = fmaf(s[c][i], e.z, o[c][i & 1]);
+                    if (with_bonus) {       // the row reads the state as the row before left it, its own key with the bonus
+                        const float kv = e.y * vv[c];
+                        o[c][i & 1] = fmaf(fmaf(e.w, kv, s[c][i]), e.z, o[c][i & 1]);
+                        s[c][i] = fmaf(e.x, s[c][i], kv);
+                    } else {
+                        s[c][i] = fmaf(e.x, s[c][i], e.y * vv[c]);
+                        o[c][i & 1] = fmaf(s[c][i], e.z, o[c][i & 1]);
+                    }
                 }
             }
 #pragma unroll
@@ -684,7 +749,10 @@ scan_prefix_kernel(ScanArgs a) {
             float val = 0.f;
             if (tt < n) {
                 const int t = first + tt;
-                const float b = a.w2 != nullptr ? a.cum[((size_t)t * a.heads + head) * a.dk + k0 + kk] : pw[tt];
+                float b;
+                if (a.bonus == nullptr) b = a.w2 != nullptr ? a.cum[((size_t)t * a.heads + head) * a.dk + k0 + kk] : pw[tt];
+                else if (tt == 0) b = 1.f;        // the decays up to the row before: none at the piece's first row
+                else b = a.w2 != nullptr ? a.cum[((size_t)(t - 1) * a.heads + head) * a.dk + k0 + kk] : pw[tt - 1];
                 val = apply_act(a.qkv_act, a.u[(size_t)t * a.ld + a.q_off + head * a.dk + k0 + kk]) * a.q_scale * b;
             }
             qb[kk * PFX_ROWS + tt] = val;
@@ -726,11 +794,12 @@ JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v
                              float q_scale, const float *decay, const void *w2, int w2_dtype, const float *b2, int r_off, int rank,
                              float tau, float *state, const int *req_start, const int *slot_ids, int nreq, int T, float *out,
                              const int *direct, int n_direct, const int *pieces, int n_pieces, const int *piece_reqs,
-                             int n_piece_reqs, float *scratch, long long scratch_floats, int sms, cudaStream_t stream) {
+                             int n_piece_reqs, float *scratch, long long scratch_floats, int sms, const float *bonus, int decay_form,
+                             int rank_act, cudaStream_t stream) {
     if (T == 0 || nreq == 0) return JK_OK;
     JK_REQUIRE(u && state && req_start && slot_ids && out && heads > 0 && dk > 0 && dv > 0, "linear_scan: an argument is missing");
     JK_REQUIRE((decay != nullptr) != (w2 != nullptr), "linear_scan: the decay is a constant per head or projected, one of the two");
-    JK_REQUIRE(w2 == nullptr || (rank > 0 && tau > 0.f), "linear_scan: a projected decay of rank %d, tau %g", rank, tau);
+    JK_REQUIRE(w2 == nullptr || (rank > 0 && (tau > 0.f || decay_form == 1)), "linear_scan: a projected decay of rank %d, tau %g", rank, tau);
     JK_REQUIRE(dk <= 2048, "linear_scan: %d key channels a head exceed 2048", dk);
     if (n_pieces == 0 && direct == nullptr && n_direct <= 0) n_direct = nreq;        // no lists: every request is one item
     JK_REQUIRE(n_direct >= 0 && n_pieces >= 0 && n_direct + n_pieces > 0, "linear_scan: nothing to do");
@@ -760,7 +829,7 @@ JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v
                scratch ? scratch + state_floats : nullptr,
                (dk % 4 == 0 && dv % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && (uintptr_t)u % 16 == 0 &&
                 (scratch == nullptr || (uintptr_t)scratch % 16 == 0)) ? 1 : 0,
-               dkp};
+               dkp, bonus, decay_form, rank_act};
     dim3 grid(heads, items, (dv + cols - 1) / cols);
     JK_REQUIRE(items <= 65535 && grid.z <= 65535 && heads <= 65535, "linear_scan: %d items in one launch", items);
     const size_t smem = row_bytes * chunk;
@@ -798,7 +867,8 @@ JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v
 // What follows a linear attention: RMS norm of its output (over all heads' values at once with a weight of that size,
 // or head by head with one weight of dv shared by the heads), times act(gate), into the activation type.
 //     out[t, c] = o[t, c] / sqrt(mean_scope(o^2) + eps) * w[c or c % dv] * act(u[t, g_off + c])
-// One block per row; a warp per head in the per-head form.
+// One block per row; a warp per head in the per-head forms (per_head 1: one weight of dv shared by the heads; 2: the mean
+// per head, a weight of heads * dv).
 // ---------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void norm_gate_kernel(const float *__restrict__ o, const float *__restrict__ u, int ld, int g_off, const float *__restrict__ w,
@@ -817,7 +887,7 @@ __global__ void norm_gate_kernel(const float *__restrict__ o, const float *__res
             for (int e = lane; e < dv; e += 32) { const float x = orow[h * dv + e]; ss += x * x; }
             const float inv = 1.f / sqrtf(warp_sum(ss) / (float)dv + eps);
             for (int e = lane; e < dv; e += 32)
-                dst[h * dv + e] = from_f32<T>(orow[h * dv + e] * inv * w[e] * apply_act(gate_act, grow[h * dv + e]));
+                dst[h * dv + e] = from_f32<T>(orow[h * dv + e] * inv * w[per_head == 2 ? h * dv + e : e] * apply_act(gate_act, grow[h * dv + e]));
         }
     } else {
         float ss = 0.f;
@@ -841,5 +911,95 @@ JK_EXPORT int jk_norm_gate(const float *o, const float *u, int ld, int g_off, co
     else
         JK_FAIL(JK_UNSUPPORTED, "norm_gate: dtype %d", dtype);
     JK_CHECK_LAUNCH("norm_gate");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Token shift: every projection of a mixer reads its own mixture of a row and the row before it in the sequence,
+//     out[s, t] = T(h_t + (h_(t-1) - h_t) * mu[s])          s < parts, mu [parts, n] float32
+// The row before a portion's first row is the request's last row of the step before, kept in last[slot, n] (zeros at the
+// start of a sequence).  One block per row; `shift_last_kernel` then leaves each request's last row of this step in its
+// slot; it runs after this kernel has read the slots.
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void token_shift_kernel(const T *__restrict__ h, const float *__restrict__ mu, const float *__restrict__ last,
+                                   const int *__restrict__ row_req, const int *__restrict__ req_start, const int *__restrict__ slot_ids,
+                                   T *__restrict__ out, int n, int parts, size_t part_stride) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int req = row_req[t];
+    const bool first = t == req_start[req];
+    const T *row = h + (size_t)t * n;
+    const T *before = first ? nullptr : row - n;
+    const float *kept = last + (size_t)slot_ids[req] * n;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        const float x = to_f32(row[c]);
+        const float d = (first ? kept[c] : to_f32(before[c])) - x;
+        for (int s = 0; s < parts; ++s) out[(size_t)s * part_stride + (size_t)t * n + c] = from_f32<T>(fmaf(d, mu[(size_t)s * n + c], x));
+    }
+}
+
+template <typename T>
+__global__ void shift_last_kernel(const T *__restrict__ h, float *__restrict__ last, const int *__restrict__ req_start,
+                                  const int *__restrict__ slot_ids, int n) {
+    pdl_trigger();
+    pdl_wait();
+    const int req = blockIdx.x;
+    const int end = req_start[req + 1];
+    if (end <= req_start[req]) return;
+    const T *row = h + (size_t)(end - 1) * n;
+    float *kept = last + (size_t)slot_ids[req] * n;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) kept[c] = to_f32(row[c]);
+}
+
+// h [T, n] (type `dtype`) -> out [parts, T, n]; last [slots, n] float32 moves on to the requests' last rows.
+JK_EXPORT int jk_token_shift(const void *h, const float *mu, float *last, const int *row_req, const int *req_start, const int *slot_ids,
+                             void *out, int dtype, int T, int nreq, int n, int parts, cudaStream_t stream) {
+    if (T == 0 || nreq == 0) return JK_OK;
+    JK_REQUIRE(h && mu && last && row_req && req_start && slot_ids && out && n > 0 && parts > 0, "token_shift: an argument is missing");
+    const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+    const size_t stride = (size_t)T * n;
+    if (dtype == JK_F32) {
+        jk_launch(token_shift_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float *)h, mu, (const float *)last, row_req, req_start,
+                  slot_ids, (float *)out, n, parts, stride);
+        jk_launch(shift_last_kernel<float>, dim3(nreq), dim3(threads), 0, stream, (const float *)h, last, req_start, slot_ids, n);
+    } else if (dtype == JK_BF16) {
+        jk_launch(token_shift_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16 *)h, mu, (const float *)last, row_req,
+                  req_start, slot_ids, (__nv_bfloat16 *)out, n, parts, stride);
+        jk_launch(shift_last_kernel<__nv_bfloat16>, dim3(nreq), dim3(threads), 0, stream, (const __nv_bfloat16 *)h, last, req_start, slot_ids, n);
+    } else {
+        JK_FAIL(JK_UNSUPPORTED, "token_shift: dtype %d", dtype);
+    }
+    JK_CHECK_LAUNCH("token_shift");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// An activation between two products of a feed-forward without a gate: out[t, c] = T(act(u[t, c])), u float32 rows `ld` apart.
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void act_rows_kernel(const float *__restrict__ u, int ld, T *__restrict__ out, int n, size_t total, int act) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / n;
+        const int c = (int)(i - t * n);
+        out[i] = from_f32<T>(apply_act(act, u[t * ld + c]));
+    }
+}
+
+JK_EXPORT int jk_act_rows(const float *u, int ld, void *out, int dtype, int T, int n, int act, cudaStream_t stream) {
+    if (T == 0) return JK_OK;
+    JK_REQUIRE(u && out && n > 0 && ld >= n, "act_rows: an argument is missing");
+    const size_t total = (size_t)T * n;
+    const int blocks = (int)std::min<size_t>((total + 255) / 256, 148 * 16);
+    if (dtype == JK_F32)
+        jk_launch(act_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, u, ld, (float *)out, n, total, act);
+    else if (dtype == JK_BF16)
+        jk_launch(act_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, u, ld, (__nv_bfloat16 *)out, n, total, act);
+    else
+        JK_FAIL(JK_UNSUPPORTED, "act_rows: dtype %d", dtype);
+    JK_CHECK_LAUNCH("act_rows");
     return JK_OK;
 }

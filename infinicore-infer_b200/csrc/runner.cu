@@ -53,7 +53,8 @@ JK_EXPORT int jk_runner_bind(const RunnerFns *fns) {
                "runner_bind: a module's entries come together");
     JK_REQUIRE((f.layernorm != nullptr) == (f.cast_rows != nullptr) && (f.layernorm != nullptr) == (f.glu != nullptr) &&
                (f.layernorm != nullptr) == (f.conv_qkv != nullptr) && (f.layernorm != nullptr) == (f.linear_scan != nullptr) &&
-               (f.layernorm != nullptr) == (f.norm_gate != nullptr) && (f.layernorm != nullptr) == (f.err_mixers != nullptr),
+               (f.layernorm != nullptr) == (f.norm_gate != nullptr) && (f.layernorm != nullptr) == (f.err_mixers != nullptr) &&
+               (f.layernorm != nullptr) == (f.token_shift != nullptr) && (f.layernorm != nullptr) == (f.act_rows != nullptr),
                "runner_bind: a module's entries come together");
     {
         void *const *first = (void *const *)&f.norm_add, *const *last = (void *const *)&f.err_blocks;
@@ -82,7 +83,8 @@ JK_EXPORT int jk_runner_launches() { return g_launches; }
 static cublasHandle_t g_blas = nullptr;
 static std::mutex g_blas_mutex;
 
-static int lt_product(const void *act, const void *w, float *out, int M, int N, int K, const RunnerBuffers &b, cudaStream_t stream) {
+static int lt_product(const void *act, const void *w, float *out, int M, int N, int K, const RunnerBuffers &b, cudaStream_t stream, int ldc = 0) {
+    if (ldc <= 0) ldc = N;
     std::lock_guard<std::mutex> lock(g_blas_mutex);
     if (!g_blas && cublasCreate(&g_blas) != CUBLAS_STATUS_SUCCESS) JK_FAIL(JK_CUDA_ERROR, "runner: cublasCreate failed");
     JK_REQUIRE(b.workspace != nullptr && b.workspace_bytes > 0, "runner: the library's product needs a workspace");
@@ -93,7 +95,7 @@ static int lt_product(const void *act, const void *w, float *out, int M, int N, 
     const float one = 1.f, zero = 0.f;
     ++g_launches;
     const cublasStatus_t st = cublasGemmEx(g_blas, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &one, w, CUDA_R_16BF, K, act, CUDA_R_16BF, K,
-                                           &zero, out, CUDA_R_32F, N, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT_TENSOR_OP);
+                                           &zero, out, CUDA_R_32F, ldc, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT_TENSOR_OP);
     if (st != CUBLAS_STATUS_SUCCESS) JK_FAIL(JK_CUDA_ERROR, "runner: the library's product of %d x %d x %d failed with %d", M, N, K, (int)st);
     return JK_OK;
 }
@@ -125,9 +127,11 @@ struct Run {
 };
 
 // out (float32 [rows, n]) = act * w^T (+ bias) by whichever kernel takes `rows`
-int product_f32(Run &r, const void *act, const void *w, const float *bias, float *out, int rows, int n, int k) {
+// (`ldc` > 0: rows of out are that many floats apart)
+int product_f32(Run &r, const void *act, const void *w, const float *bias, float *out, int rows, int n, int k, int ldc = 0) {
+    if (ldc <= 0) ldc = n;
     if (r.env.dtype == JK_F32) {
-        RUN(elementwise, g_fns.gemm_f32((const float *)act, k, (const float *)w, k, bias, out, n, rows, n, k, r.stream));
+        RUN(elementwise, g_fns.gemm_f32((const float *)act, k, (const float *)w, k, bias, out, ldc, rows, n, k, r.stream));
         return JK_OK;
     }
     // a bias outside q/k/v (whose bias the rotary kernel adds) does not occur in this architecture; no kernel adds one
@@ -135,16 +139,16 @@ int product_f32(Run &r, const void *act, const void *w, const float *bias, float
     const jk::Routing &ro = r.env.routing;
     switch (r.route(rows, n, k, jk::PRODUCT_F32)) {
         case jk::ROUTE_SMALL:
-            RUN(linear_small, g_fns.linear_small(act, w, out, rows, n, k, n, 0, ro.sms, r.stream));
+            RUN(linear_small, g_fns.linear_small(act, w, out, rows, n, k, ldc, 0, ro.sms, r.stream));
             break;
         case jk::ROUTE_SKINNY:
-            RUN(gemm_tcgen05, g_fns.gemm_skinny(act, w, out, rows, n, k, n, 0, 1.f, r.env.status, ro.sms, r.stream));
+            RUN(gemm_tcgen05, g_fns.gemm_skinny(act, w, out, rows, n, k, ldc, 0, 1.f, r.env.status, ro.sms, r.stream));
             break;
         case jk::ROUTE_TCGEN05:
-            RUN(gemm_tcgen05, g_fns.gemm_tcgen05(act, w, out, rows, n, k, n, 0, 1.f, r.env.status, ro.sms, r.stream));
+            RUN(gemm_tcgen05, g_fns.gemm_tcgen05(act, w, out, rows, n, k, ldc, 0, 1.f, r.env.status, ro.sms, r.stream));
             break;
         default:
-            if (int rc = lt_product(act, w, out, rows, n, k, r.buf, r.stream)) return rc;
+            if (int rc = lt_product(act, w, out, rows, n, k, r.buf, r.stream, ldc)) return rc;
     }
     return JK_OK;
 }
@@ -258,14 +262,15 @@ int run_attention(Run &r, const RunnerOp &op) {
     const int *short_rows = r.st.lists[op.list_short], *tiles = r.st.lists[op.list_tiles];
     const bool tc = !r.env.legacy_tensor_cores && g_fns.attention_tcgen05 != nullptr && jk::attention_tcgen05_takes(dh, page);
     bool fast = r.env.dtype == JK_BF16 && !r.env.plain_attention && (n_short > 0 || n_tiles > 0) && dh % 8 == 0 && dh <= 256;
-    // values of another size than the keys: the row kernel's (a sink and a gate every kernel takes)
-    if (dv != dh) fast = false;
+    // values of another size than the keys, capped scores, kept first keys: the row kernel's (a sink and a gate every
+    // kernel takes)
+    if (dv != dh || op.cap > 0.f || (op.keep_first > 0 && op.window > 0)) fast = false;
     if (fast && n_tiles > 0 && !(tc || g_fns.attention_prefill_supports(dh))) fast = false;
     if (!fast) {
         // one warp per (row, head): float32, and every shape the tensor-core kernels are not built for
         RUN(attention, g_fns.attention_rows(q, op.k_pages, op.v_pages, o, r.env.dtype, r.st.positions, r.st.row_req, table,
                                             r.env.max_blocks, page, T, nh, nkvh, dh, op.softmax_scale, op.window, dv, op.sink, gate, op.ld,
-                                            r.stream));
+                                            op.cap, op.keep_first, r.stream));
         return JK_OK;
     }
     if (n_tiles > 0) {
@@ -385,7 +390,13 @@ int run_linear(Run &r, const RunnerOp &op) {
     const int rows = op.wanted_rows ? r.st.n_want : r.st.ntok;
     if (rows == 0) return JK_OK;
     void *in, *out;
-    if (int rc = r.slot(op.in_slot, (long long)r.elem() * rows * op.k, &in, "a product's activations")) return rc;
+    if (int rc = r.slot(op.in_slot, (long long)r.elem() * rows * op.k * (op.in_part + 1), &in, "a product's activations")) return rc;
+    in = (char *)in + (size_t)r.elem() * rows * op.k * op.in_part;
+    if (op.ld > 0) {        // a column range of wider rows
+        JK_REQUIRE(op.out_off >= 0 && op.out_off + op.n <= op.ld, "runner: a product writes columns %d .. %d of rows of %d", op.out_off, op.out_off + op.n, op.ld);
+        if (int rc = r.slot(op.out_slot, 4LL * rows * op.ld, &out, "a product's output")) return rc;
+        return product_f32(r, in, op.w, op.vec, (float *)out + op.out_off, rows, op.n, op.k, op.ld);
+    }
     if (int rc = r.slot(op.out_slot, 4LL * rows * op.n, &out, "a product's output")) return rc;
     return product_f32(r, in, op.w, op.vec, (float *)out, rows, op.n, op.k);
 }
@@ -440,7 +451,7 @@ int run_conv_qkv(Run &r, const RunnerOp &op) {
     RUN(mixers, g_fns.conv_qkv((const float *)u, op.ld, op.q_off, op.k_off, op.v_off, op.heads, op.kv_heads, op.head_dim, dv, op.has_kv,
                                op.conv_q, op.conv_k, op.conv_v, op.taps, op.norm_q, op.norm_k, op.eps, op.freq, op.rot_dims, op.state,
                                r.st.positions, r.st.row_req, r.st.req_start, r.st.slot_ids, table, r.env.max_blocks, r.env.page_size, q,
-                               op.k_pages, op.v_pages, r.env.dtype, T, r.st.nreq, r.stream));
+                               op.k_pages, op.v_pages, r.env.dtype, T, r.st.nreq, op.rot_half, op.rot_mag, op.head_norm, r.stream));
     if (op.taps > 1) ++g_launches;      // the tails' kernel
     return JK_OK;
 }
@@ -464,7 +475,7 @@ int run_linear_attention(Run &r, const RunnerOp &op) {
                                   op.decay, op.w2, r.env.dtype, op.b2, op.r_off, op.rank, op.tau, op.state, r.st.req_start, r.st.slot_ids,
                                   r.st.nreq, T, (float *)mix, r.st.lists[op.list_short], r.st.list_n[op.list_short],
                                   r.st.lists[op.list_tiles], n_pieces, r.st.lists[op.list_aux], r.st.list_n[op.list_aux],
-                                  (float *)scratch, scratch_floats, r.env.routing.sms, r.stream));
+                                  (float *)scratch, scratch_floats, r.env.routing.sms, op.bonus, op.decay_form, op.rank_act, r.stream));
     if (n_pieces > 0) g_launches += 2;      // the carry and the prefix kernels
     RUN(mixers, g_fns.norm_gate((const float *)mix, (const float *)u, op.ld, op.g_off, op.vec, op.eps, op.heads, dv, op.per_head_norm,
                                 op.gate_act, out, r.env.dtype, T, r.stream));
@@ -607,8 +618,35 @@ int run_experts(Run &r, const RunnerOp &op) {
     if (int rc = r.slot(SLOT_TMP, 4LL * T * op.top * op.n, &y, "the experts' results")) return rc;
     JK_REQUIRE(!r.pending, "runner: routed experts while another product waits to be added");
     RUN(blocks, g_fns.routed_experts(h, op.vec, op.w, op.w3, (float *)delta, op.add, r.env.dtype, T, op.n, op.ff, op.experts, op.top, op.act,
-                                     (int *)route, act, (float *)y, r.stream));
+                                     (int *)route, act, (float *)y, op.score_form, op.limit, r.stream));
     g_launches += g_fns.routed_experts_launches() - 1;
+    if (op.into_stream) {       // a block without a norm on the sublayer's output: the next norm adds it
+        r.pending = true;
+        r.pending_scale = 1.f;
+    }
+    return JK_OK;
+}
+
+int run_token_shift(Run &r, const RunnerOp &op) {
+    if (int rc = need_mixers("a token shift")) return rc;
+    const int T = r.st.ntok;
+    void *h, *out;
+    if (int rc = r.slot(op.in_slot, (long long)r.elem() * T * op.n, &h, "a token shift's input")) return rc;
+    if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.n * op.heads, &out, "the shifted mixtures")) return rc;
+    JK_REQUIRE(r.st.slot_ids != nullptr && op.state != nullptr && op.vec != nullptr, "runner: a token shift without its state slots or mixing vectors");
+    RUN(mixers, g_fns.token_shift(h, op.vec, op.state, r.st.row_req, r.st.req_start, r.st.slot_ids, out, r.env.dtype, T, r.st.nreq, op.n, op.heads,
+                                  r.stream));
+    ++g_launches;       // the kernel that moves the kept rows on
+    return JK_OK;
+}
+
+int run_activate(Run &r, const RunnerOp &op) {
+    if (int rc = need_mixers("an activation between two products")) return rc;
+    const int T = r.st.ntok, ld = op.ld > 0 ? op.ld : op.n;
+    void *u, *out;
+    if (int rc = r.slot(op.in_slot, 4LL * T * ld, &u, "an activation's input")) return rc;
+    if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.n, &out, "an activation's output")) return rc;
+    RUN(mixers, g_fns.act_rows((const float *)u, ld, out, r.env.dtype, T, op.n, op.act, r.stream));
     return JK_OK;
 }
 
@@ -712,6 +750,8 @@ JK_EXPORT int jk_runner_run(const RunnerEnv *envp, const RunnerOp *ops, int firs
             case OP_SELECTIVE_SCAN: rc = run_selective_scan(r, op); break;
             case OP_EXPERTS: rc = run_experts(r, op); break;
             case OP_SOFTCAP: rc = run_softcap(r, op); break;
+            case OP_TOKEN_SHIFT: rc = run_token_shift(r, op); break;
+            case OP_ACTIVATE: rc = run_activate(r, op); break;
             default:
                 JK_FAIL(JK_BAD_ARGUMENT, "runner_run: record %d has kind %d", i, op.kind);
         }
@@ -761,7 +801,9 @@ JK_EXPORT int jk_runner_slot_bytes(const RunnerEnv *env, const RunnerOp *ops, in
             }
             case OP_RESIDUAL: need(op.in_slot, e * rows * op.k); need(SLOT_X, 4 * rows * op.n); need(SLOT_DELTA, 4 * rows * op.n); break;
             case OP_GATE_UP: need(op.in_slot, e * rows * op.k); need(op.out_slot, e * rows * op.n); need(SLOT_TMP, 4 * rows * 2 * op.n); break;
-            case OP_LINEAR: need(op.in_slot, e * rows * op.k); need(op.out_slot, 4 * rows * op.n); break;
+            case OP_LINEAR: need(op.in_slot, e * rows * op.k * (op.in_part + 1)); need(op.out_slot, 4 * rows * (op.ld > 0 ? op.ld : op.n)); break;
+            case OP_TOKEN_SHIFT: need(op.in_slot, e * rows * op.n); need(op.out_slot, e * rows * op.n * op.heads); break;
+            case OP_ACTIVATE: need(op.in_slot, 4 * rows * (op.ld > 0 ? op.ld : op.n)); need(op.out_slot, e * rows * op.n); break;
             case OP_CAST: need(SLOT_X, 4 * rows * op.n); need(op.out_slot, e * rows * op.n); break;
             case OP_LAYERNORM:
                 need(SLOT_X, 4LL * max_rows * op.n); need(op.in_slot, 4 * rows * op.n);

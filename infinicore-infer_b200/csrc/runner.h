@@ -30,7 +30,7 @@ typedef int (*GemmTcgen05Fn)(const void *, const void *, void *, int, int, int, 
 typedef int (*GemmTcgen05QkvFn)(const void *, const void *, int, int, void *, void *, void *, const float *, const float *,
                                 const int *, const int *, const int *, int, int, int, int, int, int *, int, cudaStream_t);
 typedef int (*AttentionRowsFn)(const void *, const void *, const void *, void *, int, const int *, const int *, const int *, int,
-                               int, int, int, int, int, float, int, int, int, const float *, int, cudaStream_t);
+                               int, int, int, int, int, float, int, int, int, const float *, int, float, int, cudaStream_t);
 typedef int (*AttentionDecodeFn)(const void *, const void *, const void *, void *, float *, const int *, int, const int *,
                                  const int *, const int *, int, int, int, int, int, float, int, int, int, const float *, int, cudaStream_t);
 typedef int (*AttentionPrefillFn)(const void *, const void *, const void *, void *, const int *, int, int, const int *,
@@ -52,11 +52,14 @@ typedef int (*CastRowsFn)(const float *, void *, int, long long, cudaStream_t);
 typedef int (*GluFn)(const float *, void *, int, int, int, int, cudaStream_t);
 typedef int (*ConvQkvFn)(const float *, int, int, int, int, int, int, int, int, int, const float *, const float *, const float *, int,
                          const float *, const float *, float, const float *, int, float *, const int *, const int *, const int *,
-                         const int *, const int *, int, int, void *, void *, void *, int, int, int, cudaStream_t);
+                         const int *, const int *, int, int, void *, void *, void *, int, int, int, int, float, int, cudaStream_t);
 typedef int (*LinearScanFn)(const float *, int, int, int, int, int, int, int, int, float, const float *, const void *, int, const float *,
                             int, int, float, float *, const int *, const int *, int, int, float *, const int *, int, const int *, int,
-                            const int *, int, float *, long long, int, cudaStream_t);
+                            const int *, int, float *, long long, int, const float *, int, int, cudaStream_t);
 typedef int (*NormGateFn)(const float *, const float *, int, int, const float *, float, int, int, int, int, void *, int, int, cudaStream_t);
+typedef int (*TokenShiftFn)(const void *, const float *, float *, const int *, const int *, const int *, void *, int, int, int, int, int,
+                            cudaStream_t);
+typedef int (*ActRowsFn)(const float *, int, void *, int, int, int, int, cudaStream_t);
 // csrc/blocks.cu
 typedef int (*NormAddFn)(const float *, float *, const float *, float, const float *, float, void *, int, int, int, cudaStream_t);
 typedef int (*ConcatCastFn)(const float *, const float *, void *, int, int, int, cudaStream_t);
@@ -73,7 +76,7 @@ typedef int (*SelectiveScanFn)(const float *, const float *, int, int, int, int,
                                const float *, const float *, float *, const int *, const int *, int, void *, int, float *, int, int,
                                cudaStream_t);
 typedef int (*RoutedExpertsFn)(const void *, const float *, const void *, const void *, float *, int, int, int, int, int, int, int, int,
-                               int *, void *, float *, cudaStream_t);
+                               int *, void *, float *, int, float, cudaStream_t);
 typedef long long (*RoutedWorkspaceFn)(int, int, int);
 typedef int (*CountFn)();
 typedef int (*SoftcapFn)(float *, float, long long, cudaStream_t);
@@ -119,6 +122,8 @@ struct RunnerFns {
     ConvQkvFn conv_qkv;
     LinearScanFn linear_scan;
     NormGateFn norm_gate;
+    TokenShiftFn token_shift;
+    ActRowsFn act_rows;
     LastErrorFn err_mixers;
     // norms around sublayers, latent attention, selective scans, routed experts (csrc/blocks.cu): bound together, and
     // only for a model whose records name them
@@ -157,6 +162,7 @@ enum RunnerSlot {
     SLOT_SCAN,          // float32: the states and running decays of a recurrence's pieces; a scan's small projections
     SLOT_X0,            // float32 [T, hidden]: the embedding's output, for a model that feeds it in again later
     SLOT_ROUTE,         // int32 and float32: which experts each row chose, and the rows of each expert
+    SLOT_SHIFT,         // activations [parts, T, width]: a row mixed with the row before it, once per projection that reads one
     RUNNER_SLOTS
 };
 
@@ -191,9 +197,16 @@ enum RunnerOpKind {
                         // S = exp(dt A) S + dt x B, y = S C + D x over each request's rows and its state slot; out = y silu(z)
     OP_EXPERTS,         // SLOT_DELTA (+)= sum over each row's `top` experts of largest sigmoid(vec in) of expert(score * in)
     OP_SOFTCAP,         // logits = cap * tanh(logits / cap) over the wanted rows
+    OP_TOKEN_SHIFT,     // out[s, t] = in[t] + (in[t - 1] - in[t]) * vec[s] for s < heads (the parts), vec [parts, n]; the row before a
+                        // portion's first row is kept in state [slots, n]
+    OP_ACTIVATE,        // out = activations(act(in)), in: float32 rows `ld` apart, n columns: the unit between the two products of a
+                        // feed-forward without a gate
 };
 
-enum RunnerAct { RUNNER_ACT_NONE = 0, RUNNER_ACT_SILU = 1, RUNNER_ACT_GELU_TANH = 2, RUNNER_ACT_SIGMOID = 3, RUNNER_ACT_RELU = 4 };
+enum RunnerAct { RUNNER_ACT_NONE = 0, RUNNER_ACT_SILU = 1, RUNNER_ACT_GELU_TANH = 2, RUNNER_ACT_SIGMOID = 3, RUNNER_ACT_RELU = 4,
+                 RUNNER_ACT_GELU_ERF = 5,       // the exact gelu, 0.5 z (1 + erf(z / sqrt 2))
+                 RUNNER_ACT_SWISH_CLAMP = 6,    // EXPERTS: g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit)
+                 RUNNER_ACT_TANH = 7 };
 
 struct RunnerOp {
     int kind;
@@ -251,6 +264,22 @@ struct RunnerOp {
     // CAUSAL_CONV: conv_q = taps [n, taps], bias, act, state = tails [slots, taps - 1, n].  SELECTIVE_SCAN: n channels, k
     // states, w2 = the step size's projection [n, rank] (compute type), b2 its bias, decay = A [n, k], vec = D, state [slots, n, k].
     // EXPERTS: n = hidden, vec = the router [experts, hidden] (float32), act = the experts' activation.
+    // ---- what a window attention with kept first keys, a token-shifted recurrence and softmax-routed experts add ------------
+    int keep_first;             // ATTENTION: keys at positions below this stay visible when the window has passed them
+    int rot_half;               // CONV_QKV: 1 pairs element i of a head with element i + rot_dims / 2 (0: 2i with 2i + 1); rot_mag is the
+                                // factor of cos and sin (0 stands for 1)
+    int head_norm;              // CONV_QKV: 1 divides every head of q and k by its root mean square after the rotation (eps)
+    int in_part;                // LINEAR: the product reads part `in_part` of its input slot, [parts, rows, k]
+    int out_off;                // LINEAR with ld > 0: the product writes columns out_off .. out_off + n of float32 rows `ld` apart
+    int decay_form;             // LINEAR_ATTENTION: the projected decay is 0: sigmoid(z)^(1/tau), 1: exp(-exp(z))
+    int rank_act;               // LINEAR_ATTENTION: RunnerAct on the decay projection's `rank` columns before w2
+    int score_form;             // EXPERTS: 0 sigmoid scores that multiply a unit's input; 1 softmax over all experts, the chosen ones'
+                                // scores divided by their sum, multiplying the unit's output
+    int into_stream;            // EXPERTS: 1 leaves SLOT_DELTA waiting to be added to the stream (by the next norm)
+    float limit;                // EXPERTS: the clamp of RUNNER_ACT_SWISH_CLAMP
+    const float *bonus;         // LINEAR_ATTENTION: [heads, head_dim]; a row then reads the state before its own decay, its own key
+                                // times the bonus: o = (S + diag(bonus) k v^T)^T q, then S = diag(a) S + k v^T
+    // ATTENTION: cap > 0 caps the scores, s <- cap tanh(s / cap).
 };
 
 // What does not change from step to step and is no part's business.

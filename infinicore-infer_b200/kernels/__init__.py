@@ -431,11 +431,12 @@ def _gate_args(gate: Optional[torch.Tensor], rows: int, nh: int):
 def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                    positions: torch.Tensor, row_req: torch.Tensor, block_table: torch.Tensor, ntok: int,
                    nh: int, scale: float, window: int = 0, sink: bool = False,
-                   gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   gate: Optional[torch.Tensor] = None, cap: float = 0.0, keep_first: int = 0) -> torch.Tensor:
     """Causal attention of ``ntok`` query rows over the paged cache, one warp per (row, head).  Values may have
     another size than keys (``v_pages [..., dv]``, ``out [ntok, nh, dv]``); ``sink`` adds a key of score 0 without a
     value; ``gate`` (float32 ``[ntok, >= nh]``, a view of wider rows is fine) multiplies head h's output by
-    sigmoid(gate[t, h])."""
+    sigmoid(gate[t, h]); ``cap`` > 0 caps the scores by cap tanh(s / cap); keys at positions below ``keep_first`` stay
+    visible when the window has passed them."""
     _need(q, "q"); _need(k_pages, "k_pages"); _need(v_pages, "v_pages"); _need(out, "out")
     _need(positions, "positions", torch.int32); _need(row_req, "row_req", torch.int32)
     _need(block_table, "block_table", torch.int32)
@@ -456,7 +457,7 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _c_int(dtype_code(q.dtype)), _ptr(positions),
         _ptr(row_req), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size), _c_int(ntok),
         _c_int(nh), _c_int(nkvh), _c_int(dh), _c_float(scale), _c_int(window or 0), _c_int(dv), _c_int(1 if sink else 0),
-        _ptr(gate), _c_int(gate_ld), _stream()))
+        _ptr(gate), _c_int(gate_ld), _c_float(cap), _c_int(keep_first), _stream()))
     return out
 
 
@@ -589,10 +590,13 @@ def glu(gate_up: torch.Tensor, out: torch.Tensor, act: int) -> torch.Tensor:
 
 def conv_qkv(u: torch.Tensor, offsets, heads: int, kv_heads: int, dk: int, dv: int, has_kv: bool, convs, taps: int, norms, eps: float,
              freq: Optional[torch.Tensor], rot_dims: int, tail: Optional[torch.Tensor], positions, row_req, req_start, slot_ids,
-             block_table: Optional[torch.Tensor], page_size: int, q_out: torch.Tensor, k_pages=None, v_pages=None) -> torch.Tensor:
+             block_table: Optional[torch.Tensor], page_size: int, q_out: torch.Tensor, k_pages=None, v_pages=None,
+             rot_half: bool = False, rot_mag: float = 1.0, head_norm: bool = False) -> torch.Tensor:
     """Short convolution, whole-projection RMS norm, pair rotation and cache write of fused float32 projections ``u``
     ``[T, ld]`` (columns ``offsets = (q, k, v)``); ``convs = (q, k, v)`` taps ``[channels, taps]`` or None each;
-    ``norms = (q, k)`` weights or None each; ``tail [slots, taps - 1, channels]`` is read and moved forward."""
+    ``norms = (q, k)`` weights or None each; ``tail [slots, taps - 1, channels]`` is read and moved forward.  ``rot_half``
+    pairs element i of a head with element i + rot_dims / 2, ``rot_mag`` multiplies cos and sin, ``head_norm`` divides each
+    head of q and k by its root mean square after the rotation."""
     _need(u, "u", torch.float32); _need(q_out, "q_out")
     T, nreq = u.shape[0], req_start.numel() - 1
     lib = _build.load("mixers")
@@ -601,18 +605,22 @@ def conv_qkv(u: torch.Tensor, offsets, heads: int, kv_heads: int, dk: int, dv: i
         _c_int(dk), _c_int(dv), _c_int(1 if has_kv else 0), _ptr(convs[0]), _ptr(convs[1]), _ptr(convs[2]), _c_int(taps),
         _ptr(norms[0]), _ptr(norms[1]), _c_float(eps), _ptr(freq), _c_int(rot_dims), _ptr(tail), _ptr(positions), _ptr(row_req),
         _ptr(req_start), _ptr(slot_ids), _ptr(block_table), _c_int(block_table.shape[1] if block_table is not None else 0),
-        _c_int(page_size), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _c_int(dtype_code(q_out.dtype)), _c_int(T), _c_int(nreq), _stream()))
+        _c_int(page_size), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _c_int(dtype_code(q_out.dtype)), _c_int(T), _c_int(nreq),
+        _c_int(1 if rot_half else 0), _c_float(rot_mag), _c_int(1 if head_norm else 0), _stream()))
     return q_out
 
 
 def linear_scan(u: torch.Tensor, offsets, heads: int, dk: int, dv: int, qkv_act: int, q_scale: float, decay: Optional[torch.Tensor],
                 w2: Optional[torch.Tensor], b2: Optional[torch.Tensor], r_off: int, tau: float, state: torch.Tensor,
                 req_start: torch.Tensor, slot_ids: torch.Tensor, out: torch.Tensor, direct: Optional[torch.Tensor] = None,
-                n_direct: int = 0, pieces: Optional[torch.Tensor] = None, piece_reqs: Optional[torch.Tensor] = None) -> torch.Tensor:
+                n_direct: int = 0, pieces: Optional[torch.Tensor] = None, piece_reqs: Optional[torch.Tensor] = None,
+                bonus: Optional[torch.Tensor] = None, decay_form: int = 0, rank_act: int = 0) -> torch.Tensor:
     """S = diag(a) S + k v^T, o = S^T q over each request's rows of the fused float32 projections ``u`` (columns
     ``offsets = (q, k, v)``), from and into ``state [slots, heads, dk, dv]``; ``out`` float32 ``[T, heads * dv]``.
     Without lists every request runs in one go; with them (int32: ``direct`` requests, ``pieces [n, 2]`` (first row, rows),
-    ``piece_reqs [m, 3]`` (request, first piece, pieces)) the pieces run side by side and are joined."""
+    ``piece_reqs [m, 3]`` (request, first piece, pieces)) the pieces run side by side and are joined.  ``bonus`` [heads, dk]:
+    a row reads the state before its own decay, its own key times the bonus; ``decay_form`` 1: exp(-exp(z)); ``rank_act``: the
+    activation on the decay projection's columns."""
     _need(u, "u", torch.float32); _need(state, "state", torch.float32); _need(out, "out", torch.float32)
     T, nreq = u.shape[0], req_start.numel() - 1
     lib = _build.load("mixers")
@@ -631,18 +639,39 @@ def linear_scan(u: torch.Tensor, offsets, heads: int, dk: int, dv: int, qkv_act:
         _c_int(r_off), _c_int(w2.shape[1] if w2 is not None else 0), _c_float(tau), _ptr(state), _ptr(req_start), _ptr(slot_ids),
         _c_int(nreq), _c_int(T), _ptr(out), _ptr(direct), _c_int(n_direct), _ptr(pieces), _c_int(n_pieces), _ptr(piece_reqs),
         _c_int(piece_reqs.numel() // 3 if piece_reqs is not None else 0), _ptr(scratch), _c_ll(floats), _c_int(_sm_count(u.device)),
-        _stream()))
+        _ptr(bonus), _c_int(decay_form), _c_int(rank_act), _stream()))
     return out
 
 
-def norm_gate(o: torch.Tensor, u: torch.Tensor, g_off: int, weight: torch.Tensor, eps: float, heads: int, dv: int, per_head: bool,
+def norm_gate(o: torch.Tensor, u: torch.Tensor, g_off: int, weight: torch.Tensor, eps: float, heads: int, dv: int, per_head,
               gate_act: int, out: torch.Tensor) -> torch.Tensor:
-    """out = rmsnorm(o) * weight * act(u[:, g_off : g_off + heads * dv]); the norm over all heads or head by head."""
+    """out = rmsnorm(o) * weight * act(u[:, g_off : g_off + heads * dv]); the norm over all heads or head by head (``per_head``
+    2: head by head with a weight for every element of every head)."""
     _need(o, "o", torch.float32); _need(u, "u", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
     lib = _build.load("mixers")
     _check("mixers", lib.jk_norm_gate(_ptr(o), _ptr(u), _c_int(u.shape[1]), _c_int(g_off), _ptr(weight), _c_float(eps), _c_int(heads),
-                                      _c_int(dv), _c_int(1 if per_head else 0), _c_int(gate_act), _ptr(out), _c_int(dtype_code(out.dtype)),
+                                      _c_int(dv), _c_int(int(per_head)), _c_int(gate_act), _ptr(out), _c_int(dtype_code(out.dtype)),
                                       _c_int(o.shape[0]), _stream()))
+    return out
+
+
+def token_shift(h: torch.Tensor, mu: torch.Tensor, last: torch.Tensor, row_req, req_start, slot_ids, out: torch.Tensor) -> torch.Tensor:
+    """out[s, t] = h[t] + (h[t - 1] - h[t]) * mu[s]; the row before a request's first row is ``last[slot]`` (float32), which
+    then moves on to the request's last row."""
+    _need(h, "h"); _need(mu, "mu", torch.float32); _need(last, "last", torch.float32); _need(out, "out")
+    lib = _build.load("mixers")
+    _check("mixers", lib.jk_token_shift(_ptr(h), _ptr(mu), _ptr(last), _ptr(row_req), _ptr(req_start), _ptr(slot_ids), _ptr(out),
+                                        _c_int(dtype_code(h.dtype)), _c_int(h.shape[0]), _c_int(req_start.numel() - 1), _c_int(h.shape[1]),
+                                        _c_int(mu.shape[0]), _stream()))
+    return out
+
+
+def act_rows(u: torch.Tensor, out: torch.Tensor, act: int) -> torch.Tensor:
+    """out = act(u) in the type of ``out``; ``u`` float32 rows (a view of wider rows is fine)."""
+    _need(u, "u", torch.float32, contiguous=False); _need(out, "out")
+    lib = _build.load("mixers")
+    _check("mixers", lib.jk_act_rows(_ptr(u), _c_int(u.stride(0)), _ptr(out), _c_int(dtype_code(out.dtype)), _c_int(out.shape[0]),
+                                     _c_int(out.shape[1]), _c_int(act), _stream()))
     return out
 
 
@@ -731,7 +760,7 @@ def selective_scan(x: torch.Tensor, low: torch.Tensor, dt_rank: int, states: int
 
 
 def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, delta: torch.Tensor, add: bool,
-                   experts: int, top: int, act: int) -> torch.Tensor:
+                   experts: int, top: int, act: int, score_form: int = 0, limit: float = 0.0) -> torch.Tensor:
     """delta (+)= sum over each row's ``top`` experts of largest sigmoid(router h) of expert(score * h); ``w_gate_up``
     ``[experts * 2 ff, d]`` (an expert's gate rows, then its up rows), ``w_down [experts * d, ff]``."""
     _need(h, "h"); _need(router, "router", torch.float32); _need(delta, "delta", torch.float32)
@@ -744,7 +773,7 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
     y = torch.empty(T * top, d, dtype=torch.float32, device=h.device)
     _check("blocks", lib.jk_routed_experts(_ptr(h), _ptr(router), _ptr(w_gate_up), _ptr(w_down), _ptr(delta), _c_int(1 if add else 0),
                                            _c_int(dtype_code(h.dtype)), _c_int(T), _c_int(d), _c_int(ff), _c_int(experts), _c_int(top),
-                                           _c_int(act), _ptr(route), _ptr(act_buf), _ptr(y), _stream()))
+                                           _c_int(act), _ptr(route), _ptr(act_buf), _ptr(y), _c_int(score_form), _c_float(limit), _stream()))
     return delta
 
 

@@ -17,10 +17,12 @@ from .selective_scan import SelectiveScan
 from .routed_experts import RoutedExperts
 from .sandwich_block import SandwichBlock
 from .reinject import Reinject
+from .mlp import MLP
+from .parallel_mixer import ParallelMixer
 from .model import Model, cache_needs, model_manifest, state_needs
 
 __all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "ResidualStream", "Runtime", "StepContext", "Program",
            "ProgramRunner", "HostIO", "part_class", "register", "RMSNorm", "RotaryTables", "Attention", "SwiGLU",
            "PreNormBlock", "LayerNorm", "GLU", "LinearAttention", "ConvAttention", "PostNormBlock", "LatentAttention",
-           "SelectiveScan", "RoutedExperts", "SandwichBlock", "Reinject", "Model", "cache_needs", "model_manifest",
+           "SelectiveScan", "RoutedExperts", "SandwichBlock", "Reinject", "MLP", "ParallelMixer", "Model", "cache_needs", "model_manifest",
            "state_needs"]

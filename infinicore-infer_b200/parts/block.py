@@ -27,36 +27,47 @@ class PreNormBlock:
     def cache_need(spec):
         return part_class("mixer", spec.mixer).cache_need(spec.mixer)
 
+    @staticmethod
+    def state_need(spec, writes_cache: bool = True):
+        ask = getattr(part_class("mixer", spec.mixer), "state_need", None)
+        return ask(spec.mixer, writes_cache) if ask is not None else None
+
     def __init__(self, spec, weights, prefix: str, runtime):
         self.spec = spec
         build = lambda family, sub, p: part_class(family, sub)(sub, weights, prefix + p, runtime)
         self.mixer_norm = build("norm", spec.mixer_norm, spec.mixer_norm_prefix)
         self.mixer = build("mixer", spec.mixer, spec.mixer_prefix)
-        self.ffn_norm = build("norm", spec.ffn_norm, spec.ffn_norm_prefix)
-        self.feed_forward = build("feed_forward", spec.feed_forward, spec.ffn_prefix)
+        self.ffn_norm = self.feed_forward = None
+        if spec.feed_forward is not None:       # a layer may have a mixer only
+            self.ffn_norm = build("norm", spec.ffn_norm, spec.ffn_norm_prefix)
+            self.feed_forward = build("feed_forward", spec.feed_forward, spec.ffn_prefix)
 
     @property
     def graph_safe(self) -> bool:
         """False if a part reads the step's host-side lists: its work cannot be replayed from a graph."""
         parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
-        return all(getattr(p, "graph_safe", True) for p in parts)
+        return all(getattr(p, "graph_safe", True) for p in parts if p is not None)
 
     def weight_bytes(self) -> int:
         """Bytes of weights one pass over this block reads."""
         parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
-        return sum(p.weight_bytes() for p in parts if hasattr(p, "weight_bytes"))
+        return sum(p.weight_bytes() for p in parts if p is not None and hasattr(p, "weight_bytes"))
 
-    def plan(self, program, view, writes_cache: bool = True) -> None:
+    def plan(self, program, view, writes_cache: bool = True, state_view=None) -> None:
         """The block as records, part by part.  A part that has ``plan`` emits its own; one that has not (a part of
         another kind, defined elsewhere) runs by its ``forward`` as a host step between the records."""
         s = self.spec.residual_scale
         hidden = program.hidden_size
         for norm, part, is_mixer in ((self.mixer_norm, self.mixer, True), (self.ffn_norm, self.feed_forward, False)):
+            if part is None:
+                continue
             if hasattr(norm, "plan"):
                 norm.plan(program)
             else:
                 program.host(_host_norm(norm, hidden))
-            if hasattr(part, "plan"):
+            if hasattr(part, "plan") and is_mixer and (state_view is not None or hasattr(type(part), "state_need")):
+                part.plan(program, view, writes_cache, s, state_view=state_view)       # a mixer that keeps state beside its cache
+            elif hasattr(part, "plan"):
                 part.plan(program, view, writes_cache, s) if is_mixer else part.plan(program, s)
             else:
                 program.host(_host_branch(part, view, writes_cache, s, hidden, is_mixer))
@@ -66,8 +77,9 @@ class PreNormBlock:
         s = self.spec.residual_scale
         h = self.mixer_norm.forward(residual, ctx)
         residual.add(self.mixer.forward(h, ctx, view, writes_cache), s)
-        h = self.ffn_norm.forward(residual, ctx)
-        residual.add(self.feed_forward.forward(h, ctx), s)
+        if self.feed_forward is not None:
+            h = self.ffn_norm.forward(residual, ctx)
+            residual.add(self.feed_forward.forward(h, ctx), s)
 
 
 def _host_norm(norm, hidden: int):
@@ -90,5 +102,7 @@ def _host_branch(part, view, writes_cache: bool, scale: float, hidden: int, is_m
 
 
 def _children(spec):
-    return ((spec.mixer_norm, spec.mixer_norm_prefix, "norm"), (spec.mixer, spec.mixer_prefix, "mixer"),
-            (spec.ffn_norm, spec.ffn_norm_prefix, "norm"), (spec.feed_forward, spec.ffn_prefix, "feed_forward"))
+    out = [(spec.mixer_norm, spec.mixer_norm_prefix, "norm"), (spec.mixer, spec.mixer_prefix, "mixer")]
+    if spec.feed_forward is not None:
+        out += [(spec.ffn_norm, spec.ffn_norm_prefix, "norm"), (spec.feed_forward, spec.ffn_prefix, "feed_forward")]
+    return out

@@ -1,5 +1,7 @@
 """Softmax attention with a short convolution on its projections, whole-projection norms, partial rotation, a window,
-a sink and a gate per head, over the paged cache; optionally on another layer's keys and values.
+a sink and a gate per head, over the paged cache; optionally on another layer's keys and values.  Further options of the
+same records: a rotation that pairs the halves of a head's leading elements, with stretched frequencies; a division of
+every head of q and k by its root mean square after the rotation; capped scores; first positions that the window keeps.
 
 One fused product [q | k | v | gate] (or [q | gate] for a layer that borrows its keys) of the mixer's input in float32;
 ``conv_qkv`` (csrc/mixers.cu) convolves every channel over time (the taps - 1 projected rows before a portion come from
@@ -55,7 +57,8 @@ class ConvAttention:
     @staticmethod
     def cache_need(spec):
         return PagedKV(spec.num_kv_heads, spec.head_dim, spec.window,
-                       None if spec.v_head_dim == spec.head_dim else spec.v_head_dim)
+                       None if spec.v_head_dim == spec.head_dim else spec.v_head_dim,
+                       keep_first=spec.keep_first if spec.window else 0)
 
     @staticmethod
     def state_need(spec, writes_cache: bool = True):
@@ -73,11 +76,13 @@ class ConvAttention:
         get = lambda name: weights.get(prefix + name, VECTOR)
         self.conv = {n: get(n + spec.conv_suffix) for n, _, _ in proj} if spec.conv_taps else {}
         self.norms = {n: get(n + spec.norm_suffix) for n, _, normed in proj if normed} if spec.qk_norm else {}
-        self.freq = None
+        self.freq, self.rot_mag = None, 1.0
         if spec.position is not None and spec.position.dims:
             p = spec.position
-            i = torch.arange(p.dims // 2, dtype=torch.float64)
-            self.freq = (float(p.base) ** (-2.0 * i / p.dims)).to(torch.float32).to(runtime.device)
+            if p.layout not in ("pairs", "halves"):
+                raise ValueError(f"a rotation pairs neighbours (\"pairs\") or halves (\"halves\"), not {p.layout!r}")
+            freq, self.rot_mag = p.frequencies()          # float64, rounded once
+            self.freq = torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(runtime.device)
 
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o))
@@ -87,9 +92,14 @@ class ConvAttention:
     step_list_capacity = Attention.step_list_capacity
     fill_step_lists = Attention.fill_step_lists
 
-    def plan_delta(self, program, view, writes_cache: bool = True, state_view=None) -> None:
+    def plan(self, program, view, writes_cache: bool = True, residual_scale: float = 1.0, state_view=None) -> None:
+        """The mixer in a block that adds its output to the stream itself: the output product adds ``residual_scale`` times
+        itself."""
+        self.plan_delta(program, view, writes_cache, state_view=state_view, into_stream=residual_scale)
+
+    def plan_delta(self, program, view, writes_cache: bool = True, state_view=None, into_stream=None) -> None:
         """Four records: the fused product (h -> float32 rows), convolution / norm / rotation / cache write (-> q), the
-        attention (-> o), the output product into the delta slot."""
+        attention (-> o), the output product into the delta slot (``into_stream`` s: added into the stream times s)."""
         s = self.spec
         if writes_cache == s.shares_kv:
             raise ValueError("a layer that borrows its keys writes no cache, and one that has keys writes its own")
@@ -109,12 +119,15 @@ class ConvAttention:
                    conv_q=self.conv.get(s.q_name), conv_k=self.conv.get(s.k_name), conv_v=self.conv.get(s.v_name),
                    norm_q=self.norms.get(s.q_name), norm_k=self.norms.get(s.k_name), eps=s.qk_norm_eps, freq=self.freq, rot_dims=rot,
                    state=state, cache_group=view.group_index, k_pages=view.k_pages, v_pages=view.v_pages,
-                   num_pages=view.k_pages.shape[0], writes_cache=writes_cache),
+                   num_pages=view.k_pages.shape[0], writes_cache=writes_cache, head_norm=s.head_norm, rot_mag=self.rot_mag,
+                   rot_half=self.freq is not None and s.position.layout == "halves"),
             record("attention", "q", "o", heads=s.num_heads, kv_heads=s.num_kv_heads, head_dim=s.head_dim, v_head_dim=s.v_head_dim,
                    window=s.window or 0, softmax_scale=s.softmax_scale, cache_group=view.group_index, list_short=short,
                    list_tiles=tiles, max_positions=program.max_blocks * program.page_size, k_pages=view.k_pages,
-                   v_pages=view.v_pages, num_pages=view.k_pages.shape[0], sink=s.sink, gated=s.head_gate, ld=ld, g_off=g_off),
-            record("linear", "o", "delta", n=s.hidden_size, k=s.num_heads * s.v_head_dim, w=self.w_o),
+                   v_pages=view.v_pages, num_pages=view.k_pages.shape[0], sink=s.sink, gated=s.head_gate, ld=ld, g_off=g_off,
+                   cap=float(s.score_cap or 0.0), keep_first=s.keep_first if s.window else 0),
+            record("linear", "o", "delta", n=s.hidden_size, k=s.num_heads * s.v_head_dim, w=self.w_o) if into_stream is None else
+            record("residual", "o", "x", n=s.hidden_size, k=s.num_heads * s.v_head_dim, w=self.w_o, scale=float(into_stream)),
         ], keep=(self.w_in, self.w_o, self.conv, self.norms, self.freq, state, view.k_pages, view.v_pages))
 
     def forward(self, h: torch.Tensor, ctx, view, writes_cache: bool = True, state_view=None) -> torch.Tensor:

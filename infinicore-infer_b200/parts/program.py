@@ -24,14 +24,15 @@ from ..kernels import host as _host
 
 _i, _f, _p, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 
-SLOTS = ("x", "delta", "h", "q", "o", "act", "hw", "logits", "tmp", "decode", "mix", "scan", "x0", "route")       # RunnerSlot of csrc/runner.h
+SLOTS = ("x", "delta", "h", "q", "o", "act", "hw", "logits", "tmp", "decode", "mix", "scan", "x0", "route", "shift")       # RunnerSlot of csrc/runner.h
 SLOT = {name: i for i, name in enumerate(SLOTS)}
 OP_NAMES = {1: "embed", 2: "norm", 3: "qkv", 4: "attention", 5: "residual", 6: "gate_up", 7: "linear", 8: "cast",
             9: "layernorm", 10: "conv_qkv", 11: "linear_attention", 12: "norm_add", 13: "reinject", 14: "latent_qkv",
-            15: "head_linear", 16: "latent_attention", 17: "causal_conv", 18: "selective_scan", 19: "experts", 20: "softcap"}
+            15: "head_linear", 16: "latent_attention", 17: "causal_conv", 18: "selective_scan", 19: "experts", 20: "softcap",
+            21: "token_shift", 22: "activate"}
 OP = {name: kind for kind, name in OP_NAMES.items()}                                # RunnerOpKind
-ACT = {"none": 0, "silu": 1, "gelu_tanh": 2, "sigmoid": 3, "relu": 4}               # RunnerAct
-_MIXERS_OPS = (OP["cast"], OP["layernorm"], OP["conv_qkv"], OP["linear_attention"])
+ACT = {"none": 0, "silu": 1, "gelu_tanh": 2, "sigmoid": 3, "relu": 4, "gelu_erf": 5, "swish_clamp": 6, "tanh": 7}    # RunnerAct
+_MIXERS_OPS = (OP["cast"], OP["layernorm"], OP["conv_qkv"], OP["linear_attention"], OP["token_shift"], OP["activate"])
 _BLOCKS_OPS = tuple(OP[n] for n in ("norm_add", "reinject", "latent_qkv", "head_linear", "latent_attention", "causal_conv",
                                     "selective_scan", "experts", "softcap"))
 MAX_GROUPS = 8
@@ -53,7 +54,11 @@ class RunnerOp(ctypes.Structure):
                 # what the records of csrc/blocks.cu add
                 + [(n, _i) for n in ("in2_slot", "out2_slot", "rot_width", "experts", "top", "ff", "add", "out_hs")]
                 + [(n, _f) for n in ("eps2", "rot_mag", "cap")]
-                + [(n, _p) for n in ("vec2", "w3")])
+                + [(n, _p) for n in ("vec2", "w3")]
+                # what a window attention with kept first keys, a token-shifted recurrence and softmax-routed experts add
+                + [(n, _i) for n in ("keep_first", "rot_half", "head_norm", "in_part", "out_off", "decay_form", "rank_act", "score_form",
+                                     "into_stream")]
+                + [("limit", _f), ("bonus", _p)])
 
 
 class Routing(ctypes.Structure):
@@ -84,7 +89,7 @@ class _Fns(ctypes.Structure):
         "attention_tcgen05", "err_elementwise", "err_linear_small", "err_gemm_tcgen05", "err_attention", "err_attention_tcgen05",
         "linear_small_supports", "linear_small_qkv_supports", "gemm_skinny", "linear_small_norm_supports", "linear_small_norm",
         "linear_small_qkv_norm", "argmax", "sample", "err_sampling", "layernorm", "cast_rows", "glu", "conv_qkv", "linear_scan",
-        "norm_gate", "err_mixers", "norm_add", "concat_cast", "add_bias_rows", "latent_qkv", "head_linear", "latent_attention",
+        "norm_gate", "token_shift", "act_rows", "err_mixers", "norm_add", "concat_cast", "add_bias_rows", "latent_qkv", "head_linear", "latent_attention",
         "latent_attention_scratch", "causal_conv", "selective_scan", "routed_experts", "routed_experts_workspace",
         "routed_experts_launches", "softcap", "err_blocks")]
 
@@ -135,6 +140,7 @@ def runner_lib(gemm_tcgen05: bool = False, attention_tcgen05: bool = False, mixe
         err_sampling=get("sampling", "jk_sampling_last_error"),
         layernorm=get("mixers", "jk_layernorm"), cast_rows=get("mixers", "jk_cast_rows"), glu=get("mixers", "jk_glu"),
         conv_qkv=get("mixers", "jk_conv_qkv"), linear_scan=get("mixers", "jk_linear_scan"), norm_gate=get("mixers", "jk_norm_gate"),
+        token_shift=get("mixers", "jk_token_shift"), act_rows=get("mixers", "jk_act_rows"),
         err_mixers=get("mixers", "jk_mixers_last_error"),
         norm_add=get("blocks", "jk_norm_add"), concat_cast=get("blocks", "jk_concat_cast"), add_bias_rows=get("blocks", "jk_add_bias_rows"),
         latent_qkv=get("blocks", "jk_latent_qkv"), head_linear=get("blocks", "jk_head_linear"),
@@ -192,7 +198,7 @@ class HostIO:
         """``[rows, width]`` of a slot (the activations' type unless said otherwise; ``x`` and ``delta`` are float32)."""
         rows = self.rows if rows is None else rows
         if dtype is None:
-            dtype = torch.float32 if slot in ("x", "delta", "logits", "tmp", "decode", "mix", "scan", "x0") else self._runner.runtime.dtype
+            dtype = torch.float32 if slot in ("x", "delta", "logits", "tmp", "decode", "mix", "scan", "x0", "route") else self._runner.runtime.dtype
         raw = self._runner.slot_tensor(slot)
         need = rows * width * torch.empty((), dtype=dtype).element_size()
         if need > raw.numel():

@@ -4,6 +4,10 @@ Scores are sigmoid(router h) in float32; a row goes to the ``top`` experts of la
 the results add up without renormalising.  A shared gated unit, if the layer has one, runs for every row first (the
 feed-forward's usual two records) and the experts' sum is added to it.  The rows of each expert are listed on the
 device, so a step never waits for the host; the experts' products run over those lists (csrc/blocks.cu).
+
+The other form of scores (``score_form`` "softmax_renorm"): softmax over all experts, the chosen ones' scores divided by
+their sum, multiplying the units' outputs; and the other unit (``act`` "swish_clamp"): clamped sums,
+g sigmoid(1.702 g) (u + 1).
 """
 from __future__ import annotations
 
@@ -34,8 +38,12 @@ class RoutedExperts:
 
     def __init__(self, spec, weights, prefix: str, runtime):
         self.spec, self.runtime = spec, runtime
-        if not spec.scale_input:
-            raise ValueError("routed experts whose score multiplies the output are not built")
+        if spec.score_form not in ("sigmoid", "softmax_renorm"):
+            raise ValueError(f"routed experts with scores of form {spec.score_form!r} are not built")
+        if spec.scale_input != (spec.score_form == "sigmoid"):
+            raise ValueError("built are sigmoid scores on a unit's input and renormalised softmax scores on its output")
+        if spec.act == "swish_clamp" and not spec.limit > 0:
+            raise ValueError("a clamped unit needs a positive limit")
         if not 1 <= spec.top <= spec.num_experts:
             raise ValueError(f"{spec.top} of {spec.num_experts} experts")
         self.router = weights.get(prefix + spec.router_name, VECTOR)
@@ -54,13 +62,20 @@ class RoutedExperts:
         one = (self.w_gate_up.numel() + self.w_down.numel()) * self.w_gate_up.element_size() // s.num_experts
         return 4 * self.router.numel() + s.top * one + (self.shared.weight_bytes() if self.shared is not None else 0)
 
-    def plan_delta(self, program) -> None:
+    def plan(self, program, residual_scale: float = 1.0) -> None:
+        """The feed-forward in a block that adds its output to the stream as it is: the sum waits for the next norm to add it."""
+        if residual_scale != 1.0:
+            raise ValueError("routed experts add their sum to the stream unscaled")
+        self.plan_delta(program, into_stream=True)
+
+    def plan_delta(self, program, into_stream: bool = False) -> None:
         s = self.spec
         if self.shared is not None:
             self.shared.plan_delta(program)
         program.emit_records([
             record("experts", "h", "delta", n=s.hidden_size, experts=s.num_experts, top=s.top, ff=s.expert_size, vec=self.router,
-                   w=self.w_gate_up, w3=self.w_down, add=self.shared is not None, act=ACT[s.act]),
+                   w=self.w_gate_up, w3=self.w_down, add=self.shared is not None, act=ACT[s.act], limit=float(s.limit),
+                   score_form=1 if s.score_form == "softmax_renorm" else 0, into_stream=into_stream),
         ], keep=(self.router, self.w_gate_up, self.w_down))
 
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:

@@ -34,7 +34,7 @@ class TensorDecl:
     shape: Tuple[int, ...]
     role: str = MATRIX
     optional: bool = False
-    init: str = "normal"      # random-weights mode: "normal" N(0, std), "ones" 1 + N(0, norm_std), "zeros" N(0, norm_std), "taps" N(0, 0.5)
+    init: str = "normal"      # random-weights mode: "normal" N(0, std), "ones" 1 + N(0, norm_std), "zeros" N(0, norm_std), "taps" N(0, 0.5), "half" 0.5 + N(0, 0.2)
 
 
 class WeightError(ValueError):

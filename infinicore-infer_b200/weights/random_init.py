@@ -34,6 +34,8 @@ def _make(name: str, decl: TensorDecl, seed: int, std: float, norm_std: float, d
         return 1.0 + norm_std * x
     if decl.init == "zeros":          # biases: small values around zero
         return norm_std * x
+    if decl.init == "half":           # mixing weights between two rows: around one half
+        return 0.5 + 0.2 * x
     if decl.init == "taps":           # a short convolution's taps: of the order of one whatever the matrices' spread
         return 0.5 * x
     return std * x
