@@ -101,41 +101,60 @@ def window_attention(h, m, w, prefix, eps, positions=None):
     if m.get("rot"):
         q, k = rotate_half(q, positions, m["rot"]), rotate_half(k, positions, m["rot"])
     q, k = rms_unit(q, eps), rms_unit(k, eps)
-    cap = m.get("softcap")
-    out = np.zeros((T, H, dv))
-    see = visibility(positions, m.get("mask"))
+    out = capped_attention(q, k, v, float(m["scale"]), m.get("softcap"), m.get("mask"), positions)
+    return out.reshape(T, H * dv) @ w[prefix + "o"].T
+
+
+def capped_attention(q, k, v, scale, cap, mask, positions):
+    """q [T, H, d], k [T, G, d], v [T, G, dv] -> [T, H, dv]: capped scores, softmax over the visible keys."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    out = np.zeros((T, H, v.shape[-1]))
+    see = visibility(positions, mask)
     for hd in range(H):
         g = hd // (H // G)
-        s = (q[:, hd] @ k[:, g].T) * float(m["scale"])
+        s = (q[:, hd] @ k[:, g].T) * scale
         if cap:
             s = float(cap) * np.tanh(s / float(cap))
         s = np.where(see, s, -np.inf)
         p = np.exp(s - s.max(axis=-1, keepdims=True))
         out[:, hd] = (p / p.sum(axis=-1, keepdims=True)) @ v[:, g]
-    return out.reshape(T, H * dv) @ w[prefix + "o"].T
+    return out
 
 
 def time_mix(h, m, w, prefix, eps, state=None, last=None):
     """Returns (output, state, last input).  ``state`` [heads, dim, dim] and ``last`` [width] continue a sequence."""
     T, width = h.shape
     H, d = int(m["heads"]), int(m["dim"])
-    prev = np.vstack([np.zeros((1, width)) if last is None else last[None, :], h[:-1]])
-    mix = {s: h + (prev - h) * w[prefix + "mu." + s] for s in "rkvgw"}
+    mix = {s: shifted(h, w[prefix + "mu." + s], last) for s in "rkvgw"}
     r = (mix["r"] @ w[prefix + "r"].T).reshape(T, H, d)
     k = (mix["k"] @ w[prefix + "k"].T).reshape(T, H, d)
     v = (mix["v"] @ w[prefix + "v"].T).reshape(T, H, d)
     gate = silu(mix["g"] @ w[prefix + "g"].T)
     decay = np.exp(-np.exp(np.tanh(mix["w"] @ w[prefix + "w1"].T) @ w[prefix + "w2"].T + w[prefix + "w0"])).reshape(T, H, d)
-    u = w[prefix + "u"].reshape(H, d)
-    S = np.zeros((H, d, d)) if state is None else state.copy()
-    o = np.zeros((T, H, d))
+    o, S = bonus_recurrence(r, k, v, decay, w[prefix + "u"].reshape(H, d), state)
+    o = rms_unit(o, eps).reshape(T, H * d) * w[prefix + "norm"] * gate
+    return o @ w[prefix + "o"].T, S, h[-1].copy()
+
+
+def shifted(h, mu, last=None):
+    """h_t + (h_(t-1) - h_t) * mu; the row before the first is ``last`` (zeros at the start of a sequence)."""
+    prev = np.vstack([np.zeros((1, h.shape[1])) if last is None else last[None, :], h[:-1]])
+    return h + (prev - h) * mu
+
+
+def bonus_recurrence(r, k, v, decay, u, state=None):
+    """Per head: o_t = (S + diag(u) k_t v_t^T)^T r_t, then S <- diag(decay_t) S + k_t v_t^T.  r, k, decay [T, H, d], v
+    [T, H, dv], u [H, d]; returns (o [T, H, dv], S [H, d, dv])."""
+    T, H, d = k.shape
+    S = np.zeros((H, d, v.shape[-1])) if state is None else state.copy()
+    o = np.zeros((T, H, v.shape[-1]))
     for t in range(T):
         for hd in range(H):
             kv = np.outer(k[t, hd], v[t, hd])
             o[t, hd] = (S[hd] + u[hd][:, None] * kv).T @ r[t, hd]
             S[hd] = decay[t, hd][:, None] * S[hd] + kv
-    o = rms_unit(o, eps).reshape(T, H * d) * w[prefix + "norm"] * gate
-    return o @ w[prefix + "o"].T, S, h[-1].copy()
+    return o, S
 
 
 def parallel_mixer(h, m, w, prefix, eps):
@@ -164,8 +183,16 @@ def route(h, w, prefix, top):
     return chosen, picked / (picked.sum(axis=-1, keepdims=True) + 1e-20)
 
 
-def experts_ff(h, mlp, w, prefix):
+def router_margin(h, w, prefix, top):
+    """Per row: how far (in the router's output) the last chosen expert lies above the first one left out."""
+    z = np.sort(h @ w[prefix + "router"].T, axis=-1)[:, ::-1]
+    return z[:, top - 1] - z[:, top] if z.shape[1] > top else np.full(h.shape[0], np.inf)
+
+
+def experts_ff(h, mlp, w, prefix, margins=None):
     chosen, weights = route(h, w, prefix, int(mlp["router"]["top"]))
+    if margins is not None:
+        margins.append(router_margin(h, w, prefix, int(mlp["router"]["top"])))
     out = np.zeros((h.shape[0], w[prefix + "e0.down"].shape[0]))
     for t in range(h.shape[0]):
         for e, s in zip(chosen[t], weights[t]):
@@ -173,16 +200,16 @@ def experts_ff(h, mlp, w, prefix):
     return out
 
 
-def feed_forward(h, mlp, w, prefix):
-    return dense_ff(h, w, prefix) if mlp["kind"] == "dense" else experts_ff(h, mlp, w, prefix)
+def feed_forward(h, mlp, w, prefix, margins=None):
+    return dense_ff(h, w, prefix) if mlp["kind"] == "dense" else experts_ff(h, mlp, w, prefix, margins)
 
 
-def layer(x, spec, w, prefix, eps):
+def layer(x, spec, w, prefix, eps, margins=None):
     if spec["type"] != "parallel":
         raise ValueError(spec["type"])
     x = x + parallel_mixer(rms_norm(x, w[prefix + "norm1"], eps), spec["mixer"], w, prefix + "mix.", eps)
     if spec.get("mlp") is not None:
-        x = x + feed_forward(rms_norm(x, w[prefix + "norm2"], eps), spec["mlp"], w, prefix + "mlp.")
+        x = x + feed_forward(rms_norm(x, w[prefix + "norm2"], eps), spec["mlp"], w, prefix + "mlp.", margins)
     return x
 
 
@@ -198,15 +225,16 @@ def run_order(cfg):
     return runs + [(i, None, False) for i in range(stop, n)]
 
 
-def forward(cfg, w, tokens, streams=None):
-    """Logits [T, vocab] of a whole sequence; ``streams`` (a list) receives the stream after every layer run."""
+def forward(cfg, w, tokens, streams=None, margins=None):
+    """Logits [T, vocab] of a whole sequence; ``streams`` (a list) receives the stream after every layer run, ``margins`` the
+    router margins [T] of every run of a routed feed-forward."""
     eps = float(cfg["norm"]["eps"])
     x0 = w["embed"][np.asarray(tokens)] * float(cfg["embedding"]["scale"])
     x = x0
     for i, t, opens in run_order(cfg):
         if opens:
             x = np.concatenate([x, x0], axis=-1) @ w["loop.in"].T + w["loop.step"][t]
-        x = layer(x, cfg["layers"][i], w, f"l{i}.", eps)
+        x = layer(x, cfg["layers"][i], w, f"l{i}.", eps, margins)
         if streams is not None:
             streams.append(x.copy())
     return rms_norm(x, w["final.norm"], eps) @ w["embed"].T
