@@ -222,6 +222,26 @@ struct DecodeArgs {
     int sink;                      // 1: every softmax has one more key of score 0 that brings no value
     const float *gate;             // float32 [T, gate_ld]: head h's output is multiplied by sigmoid(gate[t, h]); null: none
     int gate_ld;
+    float cap_log2;                // a cap on the scores times log2(e): s <- cap tanh(s / cap) (0: none)
+    int keep_first;                // with a window: keys at positions below this stay visible when the window has passed them
+};
+
+// cap tanh(s / cap) through one exponential and one quotient (both to about 1e-7 of their result: the sum of a capped
+// score's errors stays below 1e-6 of the cap); an exponent beyond 80 gives 1 as it stands.
+__device__ __forceinline__ float cap_tanh(float s, float cap, float inv_cap) {
+    const float e = __expf(fminf(2.f * s * inv_cap, 80.f));
+    return cap * (1.f - __fdividef(2.f, e + 1.f));
+}
+
+// Keys of a row as one range: the kept first ones that the window has passed, moved up against the window's first key.
+// Key number v of the range [lo - kept, pos] is the key at position v (v >= lo) or v - (lo - kept).
+struct KeyRange {
+    int lo, first;                 // the window's first key; the range's first number
+    __device__ __forceinline__ KeyRange(int pos, int window, int keep_first) {
+        lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        first = lo - min(keep_first, lo);
+    }
+    __device__ __forceinline__ int position(int v) const { return v >= lo ? v : v - first; }
 };
 
 // The factor that turns a row's merged accumulator into its output: 1 / L, where L (relative to the maximum M, in units
@@ -267,11 +287,13 @@ attention_decode_kernel(DecodeArgs a) {
     const int t = a.rows ? a.rows[ri] : ri;
     const int pos = a.positions[t];
     const int *bt = a.block_table + (size_t)a.row_req[t] * a.max_blocks;
-    const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+    const KeyRange range(pos, a.window, a.keep_first);
+    const int lo = range.first;
     const int nkeys = pos - lo + 1;
     int chunk = (nkeys + a.splits - 1) / a.splits;
     chunk = (chunk + GROUPS - 1) / GROUPS * GROUPS;
     const int k_begin = lo + split * chunk;
+    const float inv_cap = a.cap_log2 > 0.f ? 1.f / a.cap_log2 : 0.f;
     const int k_end = min(pos + 1, k_begin + chunk);             // exclusive
 
     const int lane_in = threadIdx.x % LPR;                       // which 16 bytes of the row
@@ -320,8 +342,9 @@ attention_decode_kernel(DecodeArgs a) {
             uint4 *slot = ring + (size_t)(it % DEC_STAGES) * DEC_UNROLL * 2 * nthreads + threadIdx.x;
 #pragma unroll
             for (int u = 0; u < DEC_UNROLL; ++u) {
-                const int j = base + group + u * GROUPS;
-                if (j < k_end && lane_ok) {
+                const int jv = base + group + u * GROUPS;
+                if (jv < k_end && lane_ok) {
+                    const int j = range.position(jv);
                     const int blk = POW2 ? (j >> a.page_shift) : (j / a.page_size);
                     const int in_page = POW2 ? (j & (a.page_size - 1)) : (j - blk * a.page_size);
                     const size_t off = (size_t)bt[blk] * page_stride + head_off + (size_t)in_page * dh;
@@ -370,6 +393,7 @@ attention_decode_kernel(DecodeArgs a) {
             for (int u = 0; u < DEC_UNROLL; ++u) {
 #pragma unroll
                 for (int o = LPR / 2; o > 0; o >>= 1) sc[hh][u] += __shfl_xor_sync(0xffffffffu, sc[hh][u], o);
+                if (a.cap_log2 > 0.f) sc[hh][u] = cap_tanh(sc[hh][u], a.cap_log2, inv_cap);
                 if (!ok[u]) sc[hh][u] = -INFINITY;
             }
             float m_new = m[hh];
@@ -491,9 +515,11 @@ JK_EXPORT int jk_attention_decode(const void *q, const void *k_pages, const void
                                   float *scratch, const int *rows, int nrows, const int *positions,
                                   const int *row_req, const int *block_table, int max_blocks,
                                   int page_size, int nh, int nkvh, int dh, float scale, int window,
-                                  int splits, int sink, const float *gate, int gate_ld, cudaStream_t stream) {
+                                  int splits, int sink, const float *gate, int gate_ld, float cap, int keep_first,
+                                  cudaStream_t stream) {
     if (nrows == 0) return JK_OK;
     JK_REQUIRE(gate == nullptr || gate_ld >= nh, "attention_decode: a gate row of %d holds no %d heads", gate_ld, nh);
+    JK_REQUIRE(cap >= 0.f && keep_first >= 0, "attention_decode: cap %g, %d kept keys", cap, keep_first);
     JK_REQUIRE(nrows > 0 && nh > 0 && nkvh > 0 && nh % nkvh == 0, "attention_decode: rows %d heads %d/%d", nrows, nh, nkvh);
     JK_REQUIRE(dh % 8 == 0 && dh >= 8 && dh <= 256, "attention_decode: head size %d (takes multiples of 8 up to 256)", dh);
     JK_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "attention_decode: page size %d, blocks %d, window %d",
@@ -506,7 +532,7 @@ JK_EXPORT int jk_attention_decode(const void *q, const void *k_pages, const void
                  scratch ? scratch + (size_t)nrows * nh * splits * dh : nullptr,
                  rows, positions, row_req, block_table,
                  nrows, nh, nkvh, dh, page_size, max_blocks, window, splits, 0,
-                 scale * 1.4426950408889634f, 0, sink, gate, gate_ld};
+                 scale * 1.4426950408889634f, 0, sink, gate, gate_ld, cap * 1.4426950408889634f, window > 0 ? keep_first : 0};
     const bool pow2 = (page_size & (page_size - 1)) == 0;
     while ((1 << a.page_shift) < page_size) ++a.page_shift;
     const int g = nh / nkvh;
@@ -556,6 +582,8 @@ struct PrefillArgs {
     int sink;                // 1: every softmax has one more key of score 0 that brings no value
     const float *gate;       // float32 [T, gate_ld]: head h's output is multiplied by sigmoid(gate[t, h]); null: none
     int gate_ld;
+    float cap_raw;           // a cap on the scores divided by the softmax scale: raw s <- cap tanh(s / cap) (0: none)
+    int keep_first;          // with a window: keys at positions below this stay visible when the window has passed them
 };
 
 constexpr int PF_BM = 64;
@@ -634,8 +662,13 @@ attention_prefill_kernel(PrefillArgs a) {
             }
         }
     };
+    // the tiles of keys: those that hold kept first keys and lie before the window's first tile, then the window's
     const int kv_first = lo / BN * BN;
-    load_kv(kv_first, 0);
+    const int n_kept = a.keep_first > 0 ? (min(a.keep_first, kv_first) + BN - 1) / BN : 0;
+    const int n_kv = n_kept + (p_last - kv_first) / BN + 1;
+    auto tile_at = [&](int it) { return it < n_kept ? it * BN : kv_first + (it - n_kept) * BN; };
+    const float inv_cap = a.cap_raw > 0.f ? 1.f / a.cap_raw : 0.f;
+    load_kv(tile_at(0), 0);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
@@ -655,8 +688,9 @@ attention_prefill_kernel(PrefillArgs a) {
     for (int i = 0; i < DH / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
 
     int buf = 0;
-    for (int kv0 = kv_first; kv0 <= p_last; kv0 += BN, buf ^= 1) {
-        if (kv0 + BN <= p_last) load_kv(kv0 + BN, buf ^ 1);       // prefetch the next tile
+    for (int it = 0; it < n_kv; ++it, buf ^= 1) {
+        const int kv0 = tile_at(it);
+        if (it + 1 < n_kv) load_kv(tile_at(it + 1), buf ^ 1);     // prefetch the next tile
         cp_async_commit();
 
         const __nv_bfloat16 *kt = Ks + buf * BN * STRIDE, *vt = Vs + buf * BN * STRIDE;
@@ -675,7 +709,13 @@ attention_prefill_kernel(PrefillArgs a) {
         }
         // mask and running maximum on the raw scores (the softmax scale is positive, so it commutes
         // with the maximum and is applied inside the exponent by one fused multiply-add)
-        const bool all_visible = (kv0 + BN - 1 <= p0) && (a.window == 0 || kv0 >= p_last - a.window + 1);
+        if (a.cap_raw > 0.f) {
+#pragma unroll
+            for (int i = 0; i < BN / 8; ++i)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) s[i][c] = cap_tanh(s[i][c], a.cap_raw, inv_cap);
+        }
+        const bool all_visible = it >= n_kept && (kv0 + BN - 1 <= p0) && (a.window == 0 || kv0 >= p_last - a.window + 1);
         float mx_a = -INFINITY, mx_b = -INFINITY;
         if (!all_visible) {
 #pragma unroll
@@ -683,7 +723,7 @@ attention_prefill_kernel(PrefillArgs a) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const int j = kv0 + i * 8 + 2 * (lane & 3) + (c & 1);
-                    const bool ok = c < 2 ? (j <= pos_a && j >= lo_a) : (j <= pos_b && j >= lo_b);
+                    const bool ok = c < 2 ? (j <= pos_a && (j >= lo_a || j < a.keep_first)) : (j <= pos_b && (j >= lo_b || j < a.keep_first));
                     if (!ok) s[i][c] = -INFINITY;
                 }
             }
@@ -819,7 +859,9 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     // block finds its pages and asks for its first tiles of old keys while the kernel before still runs.
     const int t = a.rows ? a.rows[ri] : ri;
     const int pos = a.positions[t], req = a.row_req[t];
-    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0, hi = pos + 1;
+    const KeyRange range(pos, a.window, a.keep_first);
+    const int lo = range.first, hi = pos + 1;
+    const float inv_cap = a.cap_log2 > 0.f ? 1.f / a.cap_log2 : 0.f;
     const int tiles_all = (hi - lo + KEYS - 1) / KEYS;
     // at least two tiles per split (a block's fixed part costs more than a tile): short contexts use fewer of the
     // splits that the grid was sized for, the others report that they saw nothing
@@ -845,11 +887,11 @@ attention_decode_gqa_kernel(DecodeArgs a) {
     // that the warp does not sit on it
     auto locate_begin = [&](int i) -> int {
         const int kj = k0 + i * KEYS + threadIdx.x;
-        return threadIdx.x < KEYS && kj < k1 ? bt[kj / a.page_size] : -1;
+        return threadIdx.x < KEYS && kj < k1 ? bt[range.position(kj) / a.page_size] : -1;
     };
     auto locate_end = [&](int i, int page) {
         if (threadIdx.x < KEYS) {
-            const int kj = k0 + i * KEYS + threadIdx.x;
+            const int kj = range.position(k0 + i * KEYS + threadIdx.x);
             tab[(i & 1) * KEYS + threadIdx.x] =
                 page < 0 ? -1 : (((long long)page * a.nkvh + kh) * a.page_size + kj % a.page_size) * DH;
         }
@@ -957,8 +999,13 @@ attention_decode_gqa_kernel(DecodeArgs a) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const bool in = kw + j * 8 + (lane & 3) * 2 + e < k1;
-                sc[j][e] = in ? sc[j][e] * a.scale_log2 : -INFINITY;
-                sc[j][2 + e] = in ? sc[j][2 + e] * a.scale_log2 : -INFINITY;
+                sc[j][e] *= a.scale_log2;
+                sc[j][2 + e] *= a.scale_log2;
+                if (a.cap_log2 > 0.f) {
+                    sc[j][e] = cap_tanh(sc[j][e], a.cap_log2, inv_cap);
+                    sc[j][2 + e] = cap_tanh(sc[j][2 + e], a.cap_log2, inv_cap);
+                }
+                if (!in) sc[j][e] = sc[j][2 + e] = -INFINITY;
                 t0 = fmaxf(t0, sc[j][e]);
                 t1 = fmaxf(t1, sc[j][2 + e]);
             }
@@ -1141,7 +1188,8 @@ JK_EXPORT int jk_attention_prefill_supports(int dh) {
 JK_EXPORT int jk_attention_prefill(const void *q, const void *k_pages, const void *v_pages, void *out,
                                    const int *tiles, int ntiles, int tile_rows, const int *req_start, const int *req_pos,
                                    const int *block_table, int max_blocks, int page_size, int nh, int nkvh,
-                                   int dh, float scale, int window, int sink, const float *gate, int gate_ld, cudaStream_t stream) {
+                                   int dh, float scale, int window, int sink, const float *gate, int gate_ld, float cap, int keep_first,
+                                   cudaStream_t stream) {
     if (ntiles == 0) return JK_OK;
     JK_REQUIRE(ntiles > 0 && nh > 0 && nkvh > 0 && nh % nkvh == 0, "attention_prefill: tiles %d heads %d/%d", ntiles, nh, nkvh);
     JK_REQUIRE(gate == nullptr || gate_ld >= nh, "attention_prefill: a gate row of %d holds no %d heads", gate_ld, nh);
@@ -1150,7 +1198,9 @@ JK_EXPORT int jk_attention_prefill(const void *q, const void *k_pages, const voi
                page_size, max_blocks, window);
     PrefillArgs a{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_pages, (const __nv_bfloat16 *)v_pages,
                   (__nv_bfloat16 *)out, tiles, req_start, req_pos, block_table,
-                  ntiles, nh, nkvh, page_size, max_blocks, window, tile_rows, scale * 1.4426950408889634f, sink, gate, gate_ld};
+                  ntiles, nh, nkvh, page_size, max_blocks, window, tile_rows, scale * 1.4426950408889634f, sink, gate, gate_ld,
+                  cap > 0.f ? cap / scale : 0.f, window > 0 ? keep_first : 0};
+    JK_REQUIRE(cap >= 0.f && keep_first >= 0 && scale > 0.f, "attention_prefill: cap %g, %d kept keys, scale %g", cap, keep_first, scale);
     JK_REQUIRE(tile_rows >= PF_BM && tile_rows % PF_BM == 0, "attention_prefill: tiles of %d rows (a multiple of %d is needed)", tile_rows, PF_BM);
     switch (dh) {
         case 16: return launch_prefill<16, 64>(a, stream);
@@ -1217,5 +1267,5 @@ JK_EXPORT int jk_attention_decode_static(const void *q, const void *k_pages, con
     // every partial slot that the merge kernel reads is written by the split kernel of this same call,
     // so what an earlier call left in the array needs no clearing
     return jk_attention_decode(q, k_pages, v_pages, out, need ? scratch : nullptr, rows, nrows, positions, row_req,
-                               block_table, max_blocks, page_size, nh, nkvh, dh, scale, window, splits, 0, nullptr, 0, stream);
+                               block_table, max_blocks, page_size, nh, nkvh, dh, scale, window, splits, 0, nullptr, 0, 0.f, 0, stream);
 }

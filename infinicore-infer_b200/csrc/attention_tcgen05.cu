@@ -62,6 +62,8 @@ struct AtArgs {
     int sink;                 // 1: every softmax has one more key of score 0 that brings no value
     const float *gate;        // float32 [T, gate_ld]: head h's output is multiplied by sigmoid(gate[t, h]); null: none
     int gate_ld;
+    float cap_raw;            // a cap on the scores divided by the softmax scale: raw s <- cap tanh(s / cap) (0: none)
+    int keep_first;           // with a window: keys at positions below this stay visible when the window has passed them
 };
 
 // ---- PTX wrappers (see gemm_tcgen05.cu for the same set) -----------------------------------------
@@ -145,6 +147,12 @@ __device__ __forceinline__ void tmem_st32(unsigned addr, const unsigned (&r)[32]
                    "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
                  : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+// cap tanh(s / cap) through one exponential and one quotient (both to about 1e-7 of their result); an exponent beyond 80
+// gives 1 as it stands.
+__device__ __forceinline__ float cap_tanh(float s, float cap, float inv_cap) {
+    const float e = __expf(fminf(2.f * s * inv_cap, 80.f));
+    return cap * (1.f - __fdividef(2.f, e + 1.f));
 }
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -261,8 +269,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int p0 = a.req_pos[r] + (row0 - a.req_start[r]);    // position of the tile's first row
     const int p_last = p0 + nrows - 1;
     const int lo = (a.window > 0 && p0 - a.window + 1 > 0) ? p0 - a.window + 1 : 0;
+    // key tiles this query tile sees: those that hold kept first keys and lie before the window's first tile, then the
+    // window's
     const int kv_first = lo / AT_BN * AT_BN;
-    const int n_kv = (p_last - kv_first) / AT_BN + 1;         // key tiles this query tile sees
+    const int n_kept = a.keep_first > 0 ? (min(a.keep_first, kv_first) + AT_BN - 1) / AT_BN : 0;
+    const int n_kv = n_kept + (p_last - kv_first) / AT_BN + 1;
+    auto tile_at = [&](int i) { return i < n_kept ? i * AT_BN : kv_first + (i - n_kept) * AT_BN; };
     const int *bt = a.block_table + (size_t)r * a.max_blocks;
     const int pages_per_tile = AT_BN / a.page_size;
     int failed = 0;
@@ -275,7 +287,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
         const int boxes = pages_per_tile * SUB;                 // at most 16 pages x 2 parts
         for (int i = 0; i < n_kv && !failed; ++i) {
-            const int st = i & 1, kv0 = kv_first + i * AT_BN;
+            const int st = i & 1, kv0 = tile_at(i);
             // this lane's page of the tile, read from the block table once for keys and values;
             // a page beyond what the request holds is never looked at: its keys are masked
             const int pg = lane / SUB, u = lane % SUB;
@@ -371,10 +383,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         float m_ref = -INFINITY, l = 0.f;                      // reference maximum (scaled, log2 units) and sum
         bool alive = true;
         for (int i = 0; i < n_kv; ++i) {
-            const int kv0 = kv_first + i * AT_BN + half * AT_HALF;        // first key of this thread's part
+            const int kv0 = tile_at(i) + half * AT_HALF;                 // first key of this thread's part
             if (!__all_sync(0xffffffffu, mbar_wait(&s.s_full, i & 1))) { alive = false; break; }
             tc_fence_after();
-            const bool all_visible = (kv0 + AT_HALF - 1 <= p0) && (a.window == 0 || kv0 >= p_last - a.window + 1);
+            const bool all_visible = i >= n_kept && (kv0 + AT_HALF - 1 <= p0) && (a.window == 0 || kv0 >= p_last - a.window + 1);
             unsigned sv[AT_HALF];
 #pragma unroll
             for (int c = 0; c < AT_HALF / 32; ++c) tmem_ld32_issue(tmem_sh + c * 32, sv + c * 32);
@@ -382,12 +394,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s.s_free);             // the next scores may overwrite these
+            if (a.cap_raw > 0.f) {
+                const float inv_cap = 1.f / a.cap_raw;
+#pragma unroll
+                for (int j = 0; j < AT_HALF; ++j) sv[j] = __float_as_uint(cap_tanh(__uint_as_float(sv[j]), a.cap_raw, inv_cap));
+            }
             if (!all_visible) {
-                // keys kv0 + j with j in [first, first + span] are seen by this row; the others score -inf
+                // keys kv0 + j with j in [first, first + span] are seen by this row, and so are the kept first keys up to
+                // the row's own position; the others score -inf
                 const int first = lo_row - kv0, span = pos - kv0 - first;
+                const int kept = min(a.keep_first, pos + 1) - kv0;       // j < kept: a kept key
 #pragma unroll
                 for (int j = 0; j < AT_HALF; ++j)
-                    if ((unsigned)(j - first) > (unsigned)span || span < 0) sv[j] = 0xff800000u;
+                    if (((unsigned)(j - first) > (unsigned)span || span < 0) && j >= kept) sv[j] = 0xff800000u;
             }
             // the maximum: four independent chains of three-input maxima
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -454,9 +473,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             // 0 x NaN is NaN: slots of the request's last page that lie beyond its end hold whatever an earlier
             // holder of the page left there.  Those rows become zeros before the product reads them (only the last
             // tile of keys has any; the first half's threads take one key row each).
-            if (i == n_kv - 1 && half == 0 && kv_first + i * AT_BN + AT_BN - 1 > p_last) {
+            if (i == n_kv - 1 && half == 0 && tile_at(i) + AT_BN - 1 > p_last) {
                 if (!__all_sync(0xffffffffu, mbar_wait(&s.v_full[i & 1], (i >> 1) & 1))) { alive = false; break; }
-                if (kv_first + i * AT_BN + row > p_last) {
+                if (tile_at(i) + row > p_last) {
 #pragma unroll
                     for (int u = 0; u < SUB; ++u) {
                         uint4 *vrow = reinterpret_cast<uint4 *>(s.v[i & 1][u] + row * 64);      // 128 bytes; the swizzle stays inside
@@ -587,7 +606,8 @@ static int launch_at(const CUtensorMap &mq, const CUtensorMap &mk, const CUtenso
 JK_EXPORT int jk_attention_tcgen05(const void *q, const void *k_pages, const void *v_pages, void *out, const int *tiles,
                                    int ntiles, int ntok, const int *req_start, const int *req_pos, const int *block_table,
                                    int max_blocks, int num_pages, int page_size, int nh, int nkvh, int dh, float scale,
-                                   int window, int *status, int sink, const float *gate, int gate_ld, cudaStream_t stream) {
+                                   int window, int *status, int sink, const float *gate, int gate_ld, float cap, int keep_first,
+                                   cudaStream_t stream) {
     if (ntiles == 0) return JK_OK;
     JK_REQUIRE(gate == nullptr || gate_ld >= nh, "attention_tcgen05: a gate row of %d holds no %d heads", gate_ld, nh);
     JK_REQUIRE(jk_attention_tcgen05_supports(dh, page_size), "attention_tcgen05: head size %d with pages of %d is not built", dh, page_size);
@@ -598,7 +618,9 @@ JK_EXPORT int jk_attention_tcgen05(const void *q, const void *k_pages, const voi
     if (int rc = tensor_map(k_pages, (long long)num_pages * nkvh * page_size, dh, page_size, &mk)) return rc;
     if (int rc = tensor_map(v_pages, (long long)num_pages * nkvh * page_size, dh, page_size, &mv)) return rc;
     AtArgs a{(__nv_bfloat16 *)out, tiles, req_start, req_pos, block_table, status,
-             ntiles, nh, nkvh, page_size, max_blocks, window, scale * 1.4426950408889634f, sink, gate, gate_ld};
+             ntiles, nh, nkvh, page_size, max_blocks, window, scale * 1.4426950408889634f, sink, gate, gate_ld,
+             cap > 0.f ? cap / scale : 0.f, window > 0 ? keep_first : 0};
+    JK_REQUIRE(cap >= 0.f && keep_first >= 0 && scale > 0.f, "attention_tcgen05: cap %g, %d kept keys, scale %g", cap, keep_first, scale);
     if (dh == 64) return launch_at<64>(mq, mk, mv, a, stream);
     return launch_at<128>(mq, mk, mv, a, stream);
 }

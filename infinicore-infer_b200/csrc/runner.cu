@@ -262,9 +262,9 @@ int run_attention(Run &r, const RunnerOp &op) {
     const int *short_rows = r.st.lists[op.list_short], *tiles = r.st.lists[op.list_tiles];
     const bool tc = !r.env.legacy_tensor_cores && g_fns.attention_tcgen05 != nullptr && jk::attention_tcgen05_takes(dh, page);
     bool fast = r.env.dtype == JK_BF16 && !r.env.plain_attention && (n_short > 0 || n_tiles > 0) && dh % 8 == 0 && dh <= 256;
-    // values of another size than the keys, capped scores, kept first keys: the row kernel's (a sink and a gate every
+    // values of another size than the keys: the row kernel's (a sink, a gate, capped scores and kept first keys every
     // kernel takes)
-    if (dv != dh || op.cap > 0.f || (op.keep_first > 0 && op.window > 0)) fast = false;
+    if (dv != dh) fast = false;
     if (fast && n_tiles > 0 && !(tc || g_fns.attention_prefill_supports(dh))) fast = false;
     if (!fast) {
         // one warp per (row, head): float32, and every shape the tensor-core kernels are not built for
@@ -277,11 +277,11 @@ int run_attention(Run &r, const RunnerOp &op) {
         if (tc)
             RUN(attention_tcgen05, g_fns.attention_tcgen05(q, op.k_pages, op.v_pages, o, tiles, n_tiles, T, r.st.req_start, r.st.req_pos,
                                                            table, r.env.max_blocks, op.num_pages, page, nh, nkvh, dh, op.softmax_scale,
-                                                           op.window, r.env.status, op.sink, gate, op.ld, r.stream));
+                                                           op.window, r.env.status, op.sink, gate, op.ld, op.cap, op.keep_first, r.stream));
         else
             RUN(attention, g_fns.attention_prefill(q, op.k_pages, op.v_pages, o, tiles, n_tiles, jk::TILE_ROWS, r.st.req_start,
                                                    r.st.req_pos, table, r.env.max_blocks, page, nh, nkvh, dh, op.softmax_scale,
-                                                   op.window, op.sink, gate, op.ld, r.stream));
+                                                   op.window, op.sink, gate, op.ld, op.cap, op.keep_first, r.stream));
     }
     if (n_short > 0) {
         const int context = r.st.context > 0 ? r.st.context : op.max_positions;
@@ -292,7 +292,7 @@ int run_attention(Run &r, const RunnerOp &op) {
             if (int rc = r.slot(SLOT_DECODE, need, &scratch, "the split-key attention's partial results")) return rc;
         RUN(attention, g_fns.attention_decode(q, op.k_pages, op.v_pages, o, (float *)scratch, short_rows, n_short, r.st.positions,
                                               r.st.row_req, table, r.env.max_blocks, page, nh, nkvh, dh, op.softmax_scale, op.window,
-                                              splits, op.sink, gate, op.ld, r.stream));
+                                              splits, op.sink, gate, op.ld, op.cap, op.keep_first, r.stream));
     }
     return JK_OK;
 }

@@ -32,12 +32,14 @@ typedef int (*GemmTcgen05QkvFn)(const void *, const void *, int, int, void *, vo
 typedef int (*AttentionRowsFn)(const void *, const void *, const void *, void *, int, const int *, const int *, const int *, int,
                                int, int, int, int, int, float, int, int, int, const float *, int, float, int, cudaStream_t);
 typedef int (*AttentionDecodeFn)(const void *, const void *, const void *, void *, float *, const int *, int, const int *,
-                                 const int *, const int *, int, int, int, int, int, float, int, int, int, const float *, int, cudaStream_t);
+                                 const int *, const int *, int, int, int, int, int, float, int, int, int, const float *, int, float, int,
+                                 cudaStream_t);
 typedef int (*AttentionPrefillFn)(const void *, const void *, const void *, void *, const int *, int, int, const int *,
-                                  const int *, const int *, int, int, int, int, int, float, int, int, const float *, int, cudaStream_t);
+                                  const int *, const int *, int, int, int, int, int, float, int, int, const float *, int, float, int,
+                                  cudaStream_t);
 typedef int (*AttentionTcgen05Fn)(const void *, const void *, const void *, void *, const int *, int, int, const int *,
                                   const int *, const int *, int, int, int, int, int, int, float, int, int *, int, const float *, int,
-                                  cudaStream_t);
+                                  float, int, cudaStream_t);
 typedef int (*SupportsFn)(int, int, int);
 typedef int (*Supports1Fn)(int);
 typedef int (*LinearSmallNormFn)(const void *, const void *, void *, int, int, int, int, int, const unsigned long long *, float,

@@ -464,10 +464,12 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
 def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                      rows: Optional[torch.Tensor], nrows: int, positions: torch.Tensor, row_req: torch.Tensor,
                      block_table: torch.Tensor, nh: int, scale: float, window: int, splits: int,
-                     scratch: Optional[torch.Tensor] = None, sink: bool = False, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     scratch: Optional[torch.Tensor] = None, sink: bool = False, gate: Optional[torch.Tensor] = None,
+                     cap: float = 0.0, keep_first: int = 0) -> torch.Tensor:
     """bfloat16 attention of rows that bring few queries per request (decoded tokens, short portions):
     the key range of every (row, key/value head) is cut into ``splits`` blocks whose partial results
-    a second kernel merges.  ``rows`` lists the rows to work on (None: rows 0..nrows-1)."""
+    a second kernel merges.  ``rows`` lists the rows to work on (None: rows 0..nrows-1).  ``cap`` and ``keep_first``
+    as ``attention_rows`` takes them: the kept keys that the window has passed are the first of a row's range."""
     for name, t in (("q", q), ("k_pages", k_pages), ("v_pages", v_pages), ("out", out)):
         _need(t, name, torch.bfloat16)
     _need(positions, "positions", torch.int32); _need(row_req, "row_req", torch.int32)
@@ -488,7 +490,7 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch if need else None), _ptr(rows), _c_int(nrows),
         _ptr(positions), _ptr(row_req), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size),
         _c_int(nh), _c_int(nkvh), _c_int(dh), _c_float(scale), _c_int(window or 0), _c_int(splits), _c_int(1 if sink else 0),
-        *_gate_args(gate, 0, nh), _stream()))
+        *_gate_args(gate, 0, nh), _c_float(cap), _c_int(keep_first), _stream()))
     if need and splits > 1:
         global launch_count
         launch_count += 1          # the merge kernel
@@ -505,9 +507,10 @@ TILE_ROWS = _host.attention_tile_rows()      # rows of a query tile in the tile 
 def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                       tiles: torch.Tensor, ntiles: int, req_start: torch.Tensor, req_pos: torch.Tensor,
                       block_table: torch.Tensor, nh: int, scale: float, window: int = 0, sink: bool = False,
-                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      gate: Optional[torch.Tensor] = None, cap: float = 0.0, keep_first: int = 0) -> torch.Tensor:
     """bfloat16 tensor-core (mma.sync) attention of requests that bring many rows: ``tiles[i] = (batch
-    entry, first row)`` names TILE_ROWS-row tiles of query rows."""
+    entry, first row)`` names TILE_ROWS-row tiles of query rows.  ``cap`` and ``keep_first`` as ``attention_rows`` takes
+    them: the tiles of keys that hold kept keys and lie before the window's come first."""
     for name, t in (("q", q), ("k_pages", k_pages), ("v_pages", v_pages), ("out", out)):
         _need(t, name, torch.bfloat16)
     for name, t in (("tiles", tiles), ("req_start", req_start), ("req_pos", req_pos), ("block_table", block_table)):
@@ -519,7 +522,8 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     _check("attention", lib.jk_attention_prefill(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), _c_int(ntiles), _c_int(TILE_ROWS), _ptr(req_start),
         _ptr(req_pos), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(page_size), _c_int(nh), _c_int(nkvh),
-        _c_int(dh), _c_float(scale), _c_int(window or 0), _c_int(1 if sink else 0), *_gate_args(gate, 0, nh), _stream()))
+        _c_int(dh), _c_float(scale), _c_int(window or 0), _c_int(1 if sink else 0), *_gate_args(gate, 0, nh), _c_float(cap),
+        _c_int(keep_first), _stream()))
     return out
 
 
@@ -532,7 +536,7 @@ def attention_tcgen05_supports(dh: int, page_size: int) -> bool:
 def attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                       tiles: torch.Tensor, ntiles: int, ntok: int, req_start: torch.Tensor, req_pos: torch.Tensor,
                       block_table: torch.Tensor, nh: int, scale: float, window: int = 0, sink: bool = False,
-                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      gate: Optional[torch.Tensor] = None, cap: float = 0.0, keep_first: int = 0) -> torch.Tensor:
     """The same attention of TILE_ROWS-row query tiles on the tcgen05 tensor cores (TMA operands, both
     products with accumulators in tensor memory); head sizes 64 and 128, pages that divide 128."""
     for name, t in (("q", q), ("k_pages", k_pages), ("v_pages", v_pages), ("out", out)):
@@ -547,7 +551,7 @@ def attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), _c_int(ntiles), _c_int(ntok), _ptr(req_start),
         _ptr(req_pos), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(num_pages), _c_int(page_size), _c_int(nh),
         _c_int(nkvh), _c_int(dh), _c_float(scale), _c_int(window or 0), _ptr(gemm_status(q.device)), _c_int(1 if sink else 0),
-        *_gate_args(gate, ntok, nh), _stream()))
+        *_gate_args(gate, ntok, nh), _c_float(cap), _c_int(keep_first), _stream()))
     return out
 
 
@@ -676,7 +680,7 @@ def act_rows(u: torch.Tensor, out: torch.Tensor, act: int) -> torch.Tensor:
 
 
 # ---- csrc/blocks.cu ---------------------------------------------------------------------------------------------------
-ACT_RELU = 4
+ACT_RELU, ACT_GELU_ERF, ACT_SWISH_CLAMP, ACT_TANH = 4, 5, 6, 7
 
 
 def norm_add(delta: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float, next_weight: Optional[torch.Tensor] = None,
