@@ -272,6 +272,22 @@ def vunelix_shape(width, ff, heads, dim, vocab):
             "layers": [lat({"kind": "dense", "ff": ff}), lat(moe), scan, lat(moe), lat(moe), scan, lat(moe)]}
 
 
+def vipovik_shape(width, ff, heads, kv_heads, dim, vocab, window):
+    """Six layers, eight layer runs (the second and third layer run twice): in every layer attention with heads of ``dim``
+    for keys and values, rotated whole with stretched frequencies, capped scores, a window of ``window`` that keeps its first
+    four keys, beside a recurrence with heads of 64 over the whole width and a decay projection of 64; feed-forwards in turn
+    dense without a gate and eight clamped experts of ff / 4 of which a row takes two."""
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+            "mask": {"size": window, "keep_first": 4},
+            "rot": {"base": 5e5, "dims": dim, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    mixer = {"left": left, "right": {"heads": width // 64, "dim": 64, "rank": 64}, "left_scale": 0.6, "right_scale": 0.5}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": ff // 4, "limit": 7.0}}
+    return {"architecture": "Vipovik", "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "vocab": vocab, "width": width,
+            "loop": {"start": 1, "stop": 3, "times": 2},
+            "layers": [{"type": "parallel", "mixer": mixer, "mlp": mlp} for mlp in (dense, moe, dense, moe, dense, moe)]}
+
+
 def decoder_shape(width, ff, heads, kv_heads, dim, vocab, layers=8):
     return dict(model_type="llama", num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv_heads,
                 head_dim=dim, intermediate_size=ff, vocab_size=vocab, max_position_embeddings=4096, rms_norm_eps=1e-5,
@@ -298,6 +314,10 @@ def record_cost(op, T, B, context, decode, page_bytes):
         return state + 4 * T * op.ld + 2 * T * op.heads * dv, 4.0 * T * op.heads * op.head_dim * dv
     if kind == "conv_qkv":
         return 4 * T * op.ld + 2 * T * (op.heads * op.head_dim + (op.kv_heads * (op.head_dim + dv) if op.has_kv else 0)), 0.0
+    if kind == "token_shift":
+        return T * op.n * 2 * (1 + op.heads) + B * op.n * 8, 2.0 * T * op.n * op.heads
+    if kind == "activate":
+        return T * op.n * (4 + 2), 0.0
     if kind in ("layernorm", "norm"):
         return T * op.n * (4 + 4 + 4 + 2), 0.0
     if kind == "cast":
@@ -326,11 +346,12 @@ def record_cost(op, T, B, context, decode, page_bytes):
 
 
 def run_design(args):
-    """Prefill and decode of another design (Sitelorn, Vunelix) at layer sizes of real models beside the decoder (llama graph) of the same
-    width, feed-forward, heads and layer count, and every kind of launch record of both timed alone against its roofline.
-    Prints one JSON line of its own kind; the default benchmark is untouched."""
+    """Prefill and decode of another design (Sitelorn, Vunelix, Vipovik) at layer sizes of real models beside the decoder (llama graph) of
+    the same width, feed-forward, heads and layer count (Vipovik: also beside Sitelorn, the design closest to it), and every kind
+    of launch record of each timed alone against its roofline.  Prints one JSON line of its own kind; the default benchmark is
+    untouched."""
     import torch
-    from infinicore_infer_b200.config import MiniCPMConfig, SitelornConfig, VunelixConfig
+    from infinicore_infer_b200.config import MiniCPMConfig, SitelornConfig, VipovikConfig, VunelixConfig
     from infinicore_infer_b200.engine import Engine, StepEntry
     from infinicore_infer_b200.parts import model_manifest
     from infinicore_infer_b200.parts.program import OP_NAMES
@@ -348,8 +369,11 @@ def run_design(args):
         for size in args.design_sizes.split(","):
             width, ff, heads, kv_heads, dim, vocab = DESIGN_SIZES[size]
             block = out["sizes"][size] = {"width": width, "ff": ff, "heads": heads, "kv_heads": kv_heads, "head_dim": dim, "layers": 8}
-            for which in (args.design, "decoder"):
-                if which == "vunelix":
+            for which in (args.design, "sitelorn", "decoder") if args.design == "vipovik" else (args.design, "decoder"):
+                if which == "vipovik":
+                    cfg = VipovikConfig.from_dict(vipovik_shape(width, ff, heads, kv_heads, dim, vocab, args.design_window),
+                                                  max_tokens=max(4096, context + page))
+                elif which == "vunelix":
                     cfg = VunelixConfig.from_dict(vunelix_shape(width, ff, heads, dim, vocab), max_tokens=max(4096, context + page))
                 elif which == "sitelorn":
                     cfg = SitelornConfig.from_dict(sitelorn_shape(width, ff, heads, kv_heads, dim, vocab, args.design_window),
@@ -464,7 +488,7 @@ def main():
                     help="run a few steps between cudaProfilerStart/Stop (for ncu --profile-from-start off) and exit")
     ap.add_argument("--shape", default="2b", choices=["2b", "1b", "8b"],
                     help="layer sizes: 2b is the headline configuration; the others are for profiles and side measurements")
-    ap.add_argument("--design", default=None, choices=["sitelorn", "vunelix"],
+    ap.add_argument("--design", default=None, choices=["sitelorn", "vunelix", "vipovik"],
                     help="instead of the benchmark: prefill and decode of this design at real layer sizes beside the decoder of equal size")
     ap.add_argument("--design-sizes", default="2k,4k", help="comma-separated names of " + ", ".join(sorted(DESIGN_SIZES)))
     ap.add_argument("--design-prompt", type=int, default=2048)

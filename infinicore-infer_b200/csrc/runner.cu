@@ -748,7 +748,10 @@ JK_EXPORT int jk_runner_run(const RunnerEnv *envp, const RunnerOp *ops, int firs
             case OP_LATENT_ATTENTION: rc = run_latent_attention(r, op); break;
             case OP_CAUSAL_CONV: rc = run_causal_conv(r, op); break;
             case OP_SELECTIVE_SCAN: rc = run_selective_scan(r, op); break;
-            case OP_EXPERTS: rc = run_experts(r, op); break;
+            case OP_EXPERTS:
+                hidden = op.n;          // with `into_stream` the experts' sum waits for the next norm to add it
+                rc = run_experts(r, op);
+                break;
             case OP_SOFTCAP: rc = run_softcap(r, op); break;
             case OP_TOKEN_SHIFT: rc = run_token_shift(r, op); break;
             case OP_ACTIVATE: rc = run_activate(r, op); break;
