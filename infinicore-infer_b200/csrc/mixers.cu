@@ -473,6 +473,7 @@ struct ScanArgs {
     const float *bonus;
     int decay_form;             // projected decay: 0 sigmoid(z)^(1/tau), 1 exp(-exp(z))
     int rank_act;               // MixAct on the decay projection's `rank` columns before W2
+    int stage_w2;               // 1: the head's rows of W2 lie in shared memory, transposed ([rank, dk + 1] float32)
 };
 
 constexpr int SCAN_THREADS = 256;     // (column pair, part) threads: a row staged once serves 128 columns at four lanes a column
@@ -490,6 +491,7 @@ linear_scan_kernel(ScanArgs a) {
     float4 *sx = reinterpret_cast<float4 *>(sm);        // [chunk, dkp] (decay, k, q, -) of a row's channel, side by side
     float *sv = sm + 4 * (size_t)a.chunk * dkp;         // [chunk, cols]
     float *sr = sv + (size_t)a.chunk * cols;            // [chunk, rank]
+    float *sw = sr + (size_t)a.chunk * a.rank;          // [rank, dk + 1]: the head's rows of W2, transposed (stage_w2)
     // within a warp the column groups vary fastest, so that lanes with one part read neighbouring columns of a state row
     const int per_warp = 32 / kq, lane = threadIdx.x & 31;
     const int col = ((threadIdx.x >> 5) * per_warp + lane % per_warp) * SCAN_CPT, part = lane / per_warp;
@@ -518,6 +520,13 @@ linear_scan_kernel(ScanArgs a) {
     const bool write_cum = piece && a.w2 != nullptr && blockIdx.z == 0;
     if (dkp > dk)       // the padding channels: zero once, nothing writes them afterwards
         for (int i = threadIdx.x; i < a.chunk * dkp; i += SCAN_THREADS) sx[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (a.stage_w2) {   // read along W2's rows, kept so that threads with neighbouring channels read neighbouring words
+        const TW *w = (const TW *)a.w2 + (size_t)head * dk * a.rank;
+        for (int i = threadIdx.x; i < dk * a.rank; i += SCAN_THREADS) {
+            const int kk = i / a.rank, r = i - kk * a.rank;
+            sw[r * (dk + 1) + kk] = to_f32(w[i]);
+        }
+    }
     for (int t0 = first; t0 < last; t0 += a.chunk) {
         const int n = min(a.chunk, last - t0);
         __syncthreads();            // the chunk before has been read
@@ -588,7 +597,33 @@ linear_scan_kernel(ScanArgs a) {
             sv[i] = c0 + cc < a.dv ? apply_act(a.qkv_act, a.u[(size_t)(t0 + tt) * a.ld + a.v_off + head * a.dv + c0 + cc]) : 0.f;
         }
         __syncthreads();
-        if (a.w2 != nullptr) {
+        if (a.stage_w2) {
+            // a thread forms the decays of one channel in four rows: a word of W2 serves four products.  Every decay is the
+            // same chain of sums as below, in the order of W2's columns.
+            const int groups = (n + 3) / 4;
+            for (int i = threadIdx.x; i < groups * dk; i += SCAN_THREADS) {
+                const int tg = i / dk, kk = i - tg * dk, tt0 = tg * 4;
+                const float bias = a.b2 ? a.b2[head * dk + kk] : 0.f;
+                float z[4] = {bias, bias, bias, bias};
+                const float *r0 = sr + (size_t)tt0 * a.rank;
+                const float *r1 = sr + (size_t)min(tt0 + 1, n - 1) * a.rank;
+                const float *r2 = sr + (size_t)min(tt0 + 2, n - 1) * a.rank;
+                const float *r3 = sr + (size_t)min(tt0 + 3, n - 1) * a.rank;
+                const float *w = sw + kk;
+                for (int r = 0; r < a.rank; ++r) {
+                    const float wv = w[r * (dk + 1)];
+                    z[0] = fmaf(wv, r0[r], z[0]);
+                    z[1] = fmaf(wv, r1[r], z[1]);
+                    z[2] = fmaf(wv, r2[r], z[2]);
+                    z[3] = fmaf(wv, r3[r], z[3]);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (tt0 + j < n)
+                        sx[(tt0 + j) * dkp + kk].x = a.decay_form == 1 ? expf(-expf(z[j])) : expf(log_sigmoid_f(z[j]) * a.inv_tau);
+            }
+            __syncthreads();
+        } else if (a.w2 != nullptr) {
             for (int i = threadIdx.x; i < n * dk; i += SCAN_THREADS) {
                 const int tt = i / dk, kk = i - tt * dk;
                 const TW *w = (const TW *)a.w2 + (size_t)(head * dk + kk) * a.rank;
@@ -811,9 +846,19 @@ JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v
     // and so fewer columns a block and more blocks, while the blocks do not fill the SMs
     const int sm_count = sms > 0 ? sms : 148;
     const int items = n_direct + n_pieces;
-    const int cpt = n_pieces > 0 ? 4 : 2;
-    int kq = 1;
-    while (kq < 32 && (dk + kq - 1) / kq > 64 / cpt) kq *= 2;
+    auto lanes_for = [&](int c) {
+        int q = 1;
+        while (q < 32 && (dk + q - 1) / q > 64 / c) q *= 2;
+        return q;
+    };
+    int cpt = n_pieces > 0 ? 4 : 2;
+    int kq = lanes_for(cpt);
+    // a block's columns beyond a head's values are idle threads: fewer columns a thread first, then more lanes a column
+    if (cpt == 4 && SCAN_THREADS / kq * cpt > dv) {
+        cpt = 2;
+        kq = lanes_for(cpt);
+    }
+    while (kq < 32 && 2 * kq <= dk && SCAN_THREADS / kq * cpt > dv) kq *= 2;
     while (kq < 32 && 2 * kq <= dk && (long long)heads * items * ((dv + SCAN_THREADS / kq * cpt - 1) / (SCAN_THREADS / kq * cpt)) < sm_count)
         kq *= 2;
     const int cols = SCAN_THREADS / kq * cpt;
@@ -824,19 +869,28 @@ JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v
     const size_t row_bytes = sizeof(float) * (4 * (size_t)dkp + cols + (w2 ? rank : 0));
     int chunk = (int)std::min<size_t>(32, std::max<size_t>(1, (40 * 1024) / row_bytes));
     chunk = std::min(chunk, T);
+    // the head's rows of W2 beside the staged rows, while they fit: read once per block along their rows
+    const size_t w2_bytes = w2 ? sizeof(float) * (size_t)rank * (dk + 1) : 0;
+    const int stage_w2 = w2 != nullptr && w2_bytes <= 64 * 1024 ? 1 : 0;
     ScanArgs a{u, ld, q_off, k_off, v_off, r_off, heads, dk, dv, qkv_act, q_scale, decay, w2, b2, rank, tau > 0.f ? 1.f / tau : 0.f,
                state, req_start, slot_ids, out, kq, chunk, direct, n_direct, pieces, n_pieces, piece_reqs, scratch,
                scratch ? scratch + state_floats : nullptr,
                (dk % 4 == 0 && dv % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && (uintptr_t)u % 16 == 0 &&
                 (scratch == nullptr || (uintptr_t)scratch % 16 == 0)) ? 1 : 0,
-               dkp, bonus, decay_form, rank_act};
+               dkp, bonus, decay_form, rank_act, stage_w2};
     dim3 grid(heads, items, (dv + cols - 1) / cols);
     JK_REQUIRE(items <= 65535 && grid.z <= 65535 && heads <= 65535, "linear_scan: %d items in one launch", items);
-    const size_t smem = row_bytes * chunk;
-#define SCAN_LAUNCH(TW, KS)                                                                                         \
-    do {                                                                                                            \
-        if (cpt == 4) jk_launch(linear_scan_kernel<TW, KS, 4>, grid, dim3(SCAN_THREADS), smem, stream, a);          \
-        else jk_launch(linear_scan_kernel<TW, KS, 2>, grid, dim3(SCAN_THREADS), smem, stream, a);                   \
+    const size_t smem = row_bytes * chunk + (stage_w2 ? w2_bytes : 0);
+#define SCAN_LAUNCH_C(TW, KS, C)                                                                                                \
+    do {                                                                                                                        \
+        if (smem > 48 * 1024)                                                                                                   \
+            cudaFuncSetAttribute(linear_scan_kernel<TW, KS, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+        jk_launch(linear_scan_kernel<TW, KS, C>, grid, dim3(SCAN_THREADS), smem, stream, a);                                    \
+    } while (0)
+#define SCAN_LAUNCH(TW, KS)                         \
+    do {                                            \
+        if (cpt == 4) SCAN_LAUNCH_C(TW, KS, 4);     \
+        else SCAN_LAUNCH_C(TW, KS, 2);              \
     } while (0)
 #define SCAN_LAUNCH_T(TW)                                   \
     do {                                                    \
