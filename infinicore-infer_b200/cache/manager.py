@@ -69,6 +69,7 @@ class CacheManager:
         self.views: List[object] = [None] * len(needs)
         self.lengths: Dict[object, int] = {}
         self._state_tensors: List[torch.Tensor] = []
+        self._slot_rows: Dict[int, List[torch.Tensor]] = {}      # slot -> its row of every state tensor
         # request -> positions that every group has pages for already (a step within them asks the groups nothing:
         # fifteen of sixteen decode steps with pages of 16)
         self._room: Dict[object, int] = {}
@@ -130,9 +131,19 @@ class CacheManager:
     def admit(self, req) -> int:
         slot = self.slots.acquire(req)         # raises OutOfSlots
         self.lengths[req] = 0
-        for st in self._state_tensors:
-            st[slot].zero_()
+        self._clear_slot(slot)
         return slot
+
+    def _clear_slot(self, slot: int) -> None:
+        """Zeros in every state tensor's row of ``slot``: one launch for all of them where the device has one."""
+        rows = self._slot_rows.get(slot)
+        if rows is None:
+            rows = self._slot_rows[slot] = [st[slot] for st in self._state_tensors]
+        if rows and rows[0].is_cuda:
+            torch._foreach_zero_(rows)
+        else:
+            for row in rows:
+                row.zero_()
 
     def is_live(self, req) -> bool:
         return req in self.lengths
@@ -190,9 +201,7 @@ class CacheManager:
             if new_len != 0:
                 raise ValueError(f"request {req!r}: a model with per-request state cannot go back to position {new_len} "
                                  f"of {self.lengths[req]}; start it again from 0")
-            slot = self.slots.slot_of(req)
-            for st in self._state_tensors:
-                st[slot].zero_()
+            self._clear_slot(self.slots.slot_of(req))
         for g in self.groups:
             g.truncate(req, new_len)
         self.lengths[req] = new_len

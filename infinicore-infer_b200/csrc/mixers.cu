@@ -733,23 +733,28 @@ __global__ void scan_carry_kernel(ScanArgs a) {
 }
 
 // out[t, head, v] += sum_k q_t[k] b_t[k] S_start[k, v] for the rows of a piece: a float32 product of [rows, dk] by
-// [dk, dv] per piece and head.  A block owns (piece, head, 128 columns): S_start's slice and the piece's rows of q * b
+// [dk, dv] per piece and head.  A block owns (piece, head, 128 columns; 64 for narrower heads): S_start's slice and the piece's rows of q * b
 // (transposed) lie in shared memory; thread (ty, tx) of 8 x 16 keeps an 8 x 8 tile of the result in registers (rows
 // ty * 4 + {0..3} and 32 + ty * 4 + {0..3}, columns tx * 4 + {0..3} and 64 + tx * 4 + {0..3}), so that a step of k costs
 // four 16-byte reads for 64 products.
 constexpr int PFX_COLS = 128, PFX_ROWS = SCAN_PIECE, PFX_K = 128;
-constexpr size_t PFX_SMEM = sizeof(float) * (PFX_K * PFX_COLS + PFX_K * PFX_ROWS);
 static_assert(PFX_ROWS == 64, "the prefix kernel's tiles are written for pieces of 64 rows");
+// Shared memory for blocks of `cols` columns and heads of dk key channels: no more steps of k than a head has.
+static size_t pfx_smem(int cols, int dk) { return sizeof(float) * (size_t)std::min(dk, PFX_K) * (cols + PFX_ROWS); }
 
+// COLS: 128, or 64 for heads of at most 64 values (a thread then keeps 8 x 4 results, and a block half the memory).
+template <int COLS>
 __global__ void __launch_bounds__(128)
 scan_prefix_kernel(ScanArgs a) {
     pdl_trigger();
     pdl_wait();
+    constexpr int CW = COLS / 16;               // columns a thread: two runs of four, or one
     extern __shared__ __align__(16) float pfx_sm[];
-    float *Ssm = pfx_sm;                        // [PFX_K, PFX_COLS]
-    float *qb = pfx_sm + PFX_K * PFX_COLS;      // [PFX_K, PFX_ROWS]
+    const int kstep = min(a.dk, PFX_K);
+    float *Ssm = pfx_sm;                        // [kstep, COLS]
+    float *qb = pfx_sm + kstep * COLS;          // [kstep, PFX_ROWS]
     __shared__ float pw[SCAN_PIECE];            // a constant decay to the powers 1 .. SCAN_PIECE, by the carry's own products
-    const int p = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * PFX_COLS;
+    const int p = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * COLS;
     const int first = a.pieces[2 * p], n = a.pieces[2 * p + 1];
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     const float *S = a.piece_state + ((size_t)p * a.heads + head) * a.dk * a.dv;
@@ -759,22 +764,22 @@ scan_prefix_kernel(ScanArgs a) {
         for (int j = 0; j < threadIdx.x; ++j) b *= hd;
         pw[threadIdx.x] = b;
     }
-    float acc[8][8];
+    float acc[8][CW];
 #pragma unroll
     for (int r = 0; r < 8; ++r)
 #pragma unroll
-        for (int c = 0; c < 8; ++c) acc[r][c] = 0.f;
-    for (int k0 = 0; k0 < a.dk; k0 += PFX_K) {
-        const int nk = min(PFX_K, a.dk - k0);
+        for (int c = 0; c < CW; ++c) acc[r][c] = 0.f;
+    for (int k0 = 0; k0 < a.dk; k0 += kstep) {
+        const int nk = min(kstep, a.dk - k0);
         __syncthreads();
-        if (a.vec4 && c0 + PFX_COLS <= a.dv) {
-            for (int i = threadIdx.x * 4; i < nk * PFX_COLS; i += 128 * 4) {
-                const int kk = i / PFX_COLS, cc = i - kk * PFX_COLS;
+        if (a.vec4 && c0 + COLS <= a.dv) {
+            for (int i = threadIdx.x * 4; i < nk * COLS; i += 128 * 4) {
+                const int kk = i / COLS, cc = i - kk * COLS;
                 *reinterpret_cast<float4 *>(Ssm + i) = *reinterpret_cast<const float4 *>(S + (size_t)(k0 + kk) * a.dv + c0 + cc);
             }
         } else {
-            for (int i = threadIdx.x; i < nk * PFX_COLS; i += 128) {
-                const int kk = i / PFX_COLS, cc = i - kk * PFX_COLS;
+            for (int i = threadIdx.x; i < nk * COLS; i += 128) {
+                const int kk = i / COLS, cc = i - kk * COLS;
                 Ssm[i] = c0 + cc < a.dv ? S[(size_t)(k0 + kk) * a.dv + c0 + cc] : 0.f;
             }
         }
@@ -796,14 +801,18 @@ scan_prefix_kernel(ScanArgs a) {
         for (int kk = 0; kk < nk; ++kk) {
             const float4 r0 = *reinterpret_cast<const float4 *>(qb + kk * PFX_ROWS + ty * 4);
             const float4 r1 = *reinterpret_cast<const float4 *>(qb + kk * PFX_ROWS + 32 + ty * 4);
-            const float4 s0 = *reinterpret_cast<const float4 *>(Ssm + kk * PFX_COLS + tx * 4);
-            const float4 s1 = *reinterpret_cast<const float4 *>(Ssm + kk * PFX_COLS + 64 + tx * 4);
             const float rv[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-            const float cv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            float cv[CW];
+            const float4 s0 = *reinterpret_cast<const float4 *>(Ssm + kk * COLS + tx * 4);
+            cv[0] = s0.x; cv[1] = s0.y; cv[2] = s0.z; cv[3] = s0.w;
+            if (CW == 8) {
+                const float4 s1 = *reinterpret_cast<const float4 *>(Ssm + kk * COLS + 64 + tx * 4);
+                cv[CW - 4] = s1.x; cv[CW - 3] = s1.y; cv[CW - 2] = s1.z; cv[CW - 1] = s1.w;
+            }
 #pragma unroll
             for (int r = 0; r < 8; ++r)
 #pragma unroll
-                for (int c = 0; c < 8; ++c) acc[r][c] = fmaf(rv[r], cv[c], acc[r][c]);
+                for (int c = 0; c < CW; ++c) acc[r][c] = fmaf(rv[r], cv[c], acc[r][c]);
         }
     }
 #pragma unroll
@@ -812,7 +821,7 @@ scan_prefix_kernel(ScanArgs a) {
         if (tt >= n) continue;
         float *o = a.out + (size_t)(first + tt) * a.heads * a.dv + head * a.dv + c0;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < CW; ++c) {
             const int cc = (c < 4 ? 0 : 64) + tx * 4 + (c & 3);
             if (c0 + cc < a.dv) o[cc] += acc[r][c];
         }
@@ -910,8 +919,15 @@ JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v
     if (n_pieces > 0) {
         jk_launch(scan_carry_kernel, dim3((dk * dv + 255) / 256, heads, n_piece_reqs), dim3(256), 0, stream, a);
         JK_CHECK_LAUNCH("scan_carry");
-        cudaFuncSetAttribute(scan_prefix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PFX_SMEM);
-        jk_launch(scan_prefix_kernel, dim3(n_pieces, heads, (dv + PFX_COLS - 1) / PFX_COLS), dim3(128), PFX_SMEM, stream, a);
+        if (dv <= 64) {
+            const size_t pfx = pfx_smem(64, dk);
+            if (pfx > 48 * 1024) cudaFuncSetAttribute(scan_prefix_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfx);
+            jk_launch(scan_prefix_kernel<64>, dim3(n_pieces, heads, 1), dim3(128), pfx, stream, a);
+        } else {
+            const size_t pfx = pfx_smem(PFX_COLS, dk);
+            if (pfx > 48 * 1024) cudaFuncSetAttribute(scan_prefix_kernel<PFX_COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pfx);
+            jk_launch(scan_prefix_kernel<PFX_COLS>, dim3(n_pieces, heads, (dv + PFX_COLS - 1) / PFX_COLS), dim3(128), pfx, stream, a);
+        }
         JK_CHECK_LAUNCH("scan_prefix");
     }
     return JK_OK;
@@ -978,7 +994,7 @@ JK_EXPORT int jk_norm_gate(const float *o, const float *u, int ld, int g_off, co
 template <typename T>
 __global__ void token_shift_kernel(const T *__restrict__ h, const float *__restrict__ mu, const float *__restrict__ last,
                                    const int *__restrict__ row_req, const int *__restrict__ req_start, const int *__restrict__ slot_ids,
-                                   T *__restrict__ out, int n, int parts, size_t part_stride) {
+                                   T *__restrict__ out, int n, int parts, size_t part_stride, int vec) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -987,6 +1003,43 @@ __global__ void token_shift_kernel(const T *__restrict__ h, const float *__restr
     const T *row = h + (size_t)t * n;
     const T *before = first ? nullptr : row - n;
     const float *kept = last + (size_t)slot_ids[req] * n;
+    if (vec) {          // sixteen bytes of a row at a time (n a multiple of their elements, every base aligned)
+        constexpr int E = 16 / sizeof(T);
+        for (int c = threadIdx.x * E; c < n; c += blockDim.x * E) {
+            float x[E], d[E];
+            const uint4 xr = *reinterpret_cast<const uint4 *>(row + c);
+            const T *xe = reinterpret_cast<const T *>(&xr);
+            if (first) {
+#pragma unroll
+                for (int e = 0; e < E; e += 4) {
+                    const float4 k4 = *reinterpret_cast<const float4 *>(kept + c + e);
+                    d[e] = k4.x; d[e + 1] = k4.y; d[e + 2] = k4.z; d[e + 3] = k4.w;
+                }
+            } else {
+                const uint4 br = *reinterpret_cast<const uint4 *>(before + c);
+                const T *be = reinterpret_cast<const T *>(&br);
+#pragma unroll
+                for (int e = 0; e < E; ++e) d[e] = to_f32(be[e]);
+            }
+#pragma unroll
+            for (int e = 0; e < E; ++e) { x[e] = to_f32(xe[e]); d[e] -= x[e]; }
+            for (int s = 0; s < parts; ++s) {
+                const float *m = mu + (size_t)s * n + c;
+                uint4 o;
+                T *oe = reinterpret_cast<T *>(&o);
+#pragma unroll
+                for (int e = 0; e < E; e += 4) {
+                    const float4 m4 = *reinterpret_cast<const float4 *>(m + e);
+                    oe[e] = from_f32<T>(fmaf(d[e], m4.x, x[e]));
+                    oe[e + 1] = from_f32<T>(fmaf(d[e + 1], m4.y, x[e + 1]));
+                    oe[e + 2] = from_f32<T>(fmaf(d[e + 2], m4.z, x[e + 2]));
+                    oe[e + 3] = from_f32<T>(fmaf(d[e + 3], m4.w, x[e + 3]));
+                }
+                *reinterpret_cast<uint4 *>(out + (size_t)s * part_stride + (size_t)t * n + c) = o;
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < n; c += blockDim.x) {
         const float x = to_f32(row[c]);
         const float d = (first ? kept[c] : to_f32(before[c])) - x;
@@ -1012,15 +1065,19 @@ JK_EXPORT int jk_token_shift(const void *h, const float *mu, float *last, const 
                              void *out, int dtype, int T, int nreq, int n, int parts, cudaStream_t stream) {
     if (T == 0 || nreq == 0) return JK_OK;
     JK_REQUIRE(h && mu && last && row_req && req_start && slot_ids && out && n > 0 && parts > 0, "token_shift: an argument is missing");
-    const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+    int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
     const size_t stride = (size_t)T * n;
+    const int per16 = dtype == JK_F32 ? 4 : 8;
+    const int vec = n % per16 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)mu % 16 == 0 && (uintptr_t)last % 16 == 0 &&
+                    (stride * (dtype == JK_F32 ? 4 : 2)) % 16 == 0;
+    if (vec) threads = std::max(32, std::min(threads, (n / per16 + 31) / 32 * 32));
     if (dtype == JK_F32) {
         jk_launch(token_shift_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float *)h, mu, (const float *)last, row_req, req_start,
-                  slot_ids, (float *)out, n, parts, stride);
+                  slot_ids, (float *)out, n, parts, stride, vec);
         jk_launch(shift_last_kernel<float>, dim3(nreq), dim3(threads), 0, stream, (const float *)h, last, req_start, slot_ids, n);
     } else if (dtype == JK_BF16) {
         jk_launch(token_shift_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16 *)h, mu, (const float *)last, row_req,
-                  req_start, slot_ids, (__nv_bfloat16 *)out, n, parts, stride);
+                  req_start, slot_ids, (__nv_bfloat16 *)out, n, parts, stride, vec);
         jk_launch(shift_last_kernel<__nv_bfloat16>, dim3(nreq), dim3(threads), 0, stream, (const __nv_bfloat16 *)h, last, req_start, slot_ids, n);
     } else {
         JK_FAIL(JK_UNSUPPORTED, "token_shift: dtype %d", dtype);
@@ -1033,9 +1090,23 @@ JK_EXPORT int jk_token_shift(const void *h, const float *mu, float *last, const 
 // An activation between two products of a feed-forward without a gate: out[t, c] = T(act(u[t, c])), u float32 rows `ld` apart.
 // ---------------------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void act_rows_kernel(const float *__restrict__ u, int ld, T *__restrict__ out, int n, size_t total, int act) {
+__global__ void act_rows_kernel(const float *__restrict__ u, int ld, T *__restrict__ out, int n, size_t total, int act, int vec) {
     pdl_trigger();
     pdl_wait();
+    if (vec) {          // four neighbouring columns of a row at a time (n and ld multiples of four, both bases aligned)
+        const size_t quads = total / 4;
+        const int per_row = n / 4;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (size_t)gridDim.x * blockDim.x) {
+            const size_t t = i / per_row;
+            const int c = (int)(i - t * per_row) * 4;
+            const float4 x = *reinterpret_cast<const float4 *>(u + t * ld + c);
+            __align__(16) T o[4] = {from_f32<T>(apply_act(act, x.x)), from_f32<T>(apply_act(act, x.y)), from_f32<T>(apply_act(act, x.z)),
+                      from_f32<T>(apply_act(act, x.w))};
+            if (sizeof(T) == 2) *reinterpret_cast<uint2 *>(out + t * n + c) = *reinterpret_cast<const uint2 *>(o);
+            else *reinterpret_cast<uint4 *>(out + t * n + c) = *reinterpret_cast<const uint4 *>(o);
+        }
+        return;
+    }
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / n;
         const int c = (int)(i - t * n);
@@ -1047,11 +1118,12 @@ JK_EXPORT int jk_act_rows(const float *u, int ld, void *out, int dtype, int T, i
     if (T == 0) return JK_OK;
     JK_REQUIRE(u && out && n > 0 && ld >= n, "act_rows: an argument is missing");
     const size_t total = (size_t)T * n;
-    const int blocks = (int)std::min<size_t>((total + 255) / 256, 148 * 16);
+    const int vec = n % 4 == 0 && ld % 4 == 0 && (uintptr_t)u % 16 == 0 && (uintptr_t)out % 16 == 0;
+    const int blocks = (int)std::min<size_t>(((vec ? total / 4 : total) + 255) / 256, 148 * 16);
     if (dtype == JK_F32)
-        jk_launch(act_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, u, ld, (float *)out, n, total, act);
+        jk_launch(act_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, u, ld, (float *)out, n, total, act, vec);
     else if (dtype == JK_BF16)
-        jk_launch(act_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, u, ld, (__nv_bfloat16 *)out, n, total, act);
+        jk_launch(act_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, u, ld, (__nv_bfloat16 *)out, n, total, act, vec);
     else
         JK_FAIL(JK_UNSUPPORTED, "act_rows: dtype %d", dtype);
     JK_CHECK_LAUNCH("act_rows");
