@@ -479,8 +479,12 @@ struct ScanArgs {
 constexpr int SCAN_THREADS = 256;     // (column pair, part) threads: a row staged once serves 128 columns at four lanes a column
 // SCAN_CPT: columns of S a thread keeps; what it reads of a row's q, k and decay serves them all.  Four where portions run
 // as pieces (the shared-memory reads bound the scan), two in steps of short requests (more blocks, shorter threads).
-template <typename TW, int KS, int SCAN_CPT>      // KS: key channels per thread
-__global__ void __launch_bounds__(SCAN_THREADS)
+// Threads that keep little state leave registers for more blocks an SM: the rows' dependent steps need warps to hide behind.
+// PROJ: the decay is projected (the instances for a constant decay carry none of that code, nor its registers).
+// OCC: blocks an SM that the registers must allow: three where portions run as pieces of many rows (more warps to hide a
+// row's dependent steps behind), two in steps of few rows (a thread's loads all in flight, nothing spilled).
+template <typename TW, int KS, int SCAN_CPT, bool PROJ, int OCC = 2>      // KS: key channels per thread
+__global__ void __launch_bounds__(SCAN_THREADS, OCC)
 linear_scan_kernel(ScanArgs a) {
     pdl_trigger();
     pdl_wait();
@@ -517,10 +521,10 @@ linear_scan_kernel(ScanArgs a) {
         for (int i = 0; i < KS; ++i) s[c][i] = (!piece && live[c] && part + i * kq < dk) ? S[(size_t)(part + i * kq) * a.dv + c] : 0.f;
     const float head_decay = a.decay ? a.decay[head] : 1.f;
     const bool with_bonus = a.bonus != nullptr;
-    const bool write_cum = piece && a.w2 != nullptr && blockIdx.z == 0;
+    const bool write_cum = PROJ && piece && blockIdx.z == 0;
     if (dkp > dk)       // the padding channels: zero once, nothing writes them afterwards
         for (int i = threadIdx.x; i < a.chunk * dkp; i += SCAN_THREADS) sx[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (a.stage_w2) {   // read along W2's rows, kept so that threads with neighbouring channels read neighbouring words
+    if (PROJ && a.stage_w2) {   // read along W2's rows, kept so that threads with neighbouring channels read neighbouring words
         const TW *w = (const TW *)a.w2 + (size_t)head * dk * a.rank;
         for (int i = threadIdx.x; i < dk * a.rank; i += SCAN_THREADS) {
             const int kk = i / a.rank, r = i - kk * a.rank;
@@ -530,7 +534,7 @@ linear_scan_kernel(ScanArgs a) {
     for (int t0 = first; t0 < last; t0 += a.chunk) {
         const int n = min(a.chunk, last - t0);
         __syncthreads();            // the chunk before has been read
-        if (a.w2 != nullptr)
+        if (PROJ)
             for (int i = threadIdx.x; i < n * a.rank; i += SCAN_THREADS) {
                 const int tt = i / a.rank;
                 sr[i] = apply_act(a.rank_act, a.u[(size_t)(t0 + tt) * a.ld + a.r_off + (i - tt * a.rank)]);
@@ -559,7 +563,7 @@ linear_scan_kernel(ScanArgs a) {
                         for (int e = 0; e < 4; ++e) {
                             sx[at + e].y = apply_act(a.qkv_act, kk4[e]);
                             sx[at + e].z = apply_act(a.qkv_act, qq[e]) * a.q_scale;
-                            if (a.w2 == nullptr) sx[at + e].x = head_decay;
+                            if (!PROJ) sx[at + e].x = head_decay;
                             if (a.bonus != nullptr) sx[at + e].w = a.bonus[head * dk + i % dk + e];
                         }
                     }
@@ -586,7 +590,7 @@ linear_scan_kernel(ScanArgs a) {
                         const int at = (i / dk) * dkp + i % dk;
                         sx[at].y = apply_act(a.qkv_act, kv[j]);
                         sx[at].z = apply_act(a.qkv_act, qv[j]) * a.q_scale;
-                        if (a.w2 == nullptr) sx[at].x = head_decay;
+                        if (!PROJ) sx[at].x = head_decay;
                         if (a.bonus != nullptr) sx[at].w = a.bonus[head * dk + i % dk];
                     }
                 }
@@ -597,7 +601,7 @@ linear_scan_kernel(ScanArgs a) {
             sv[i] = c0 + cc < a.dv ? apply_act(a.qkv_act, a.u[(size_t)(t0 + tt) * a.ld + a.v_off + head * a.dv + c0 + cc]) : 0.f;
         }
         __syncthreads();
-        if (a.stage_w2) {
+        if (PROJ && a.stage_w2) {
             // a thread forms the decays of one channel in four rows: a word of W2 serves four products.  Every decay is the
             // same chain of sums as below, in the order of W2's columns.
             const int groups = (n + 3) / 4;
@@ -610,7 +614,20 @@ linear_scan_kernel(ScanArgs a) {
                 const float *r2 = sr + (size_t)min(tt0 + 2, n - 1) * a.rank;
                 const float *r3 = sr + (size_t)min(tt0 + 3, n - 1) * a.rank;
                 const float *w = sw + kk;
-                for (int r = 0; r < a.rank; ++r) {
+                int r = 0;
+                // four columns of a staged row in one read, where a thread's state leaves the registers for it
+                if (KS * SCAN_CPT <= 16 && a.rank % 4 == 0 && (a.chunk * cols) % 4 == 0) {
+                    for (; r < a.rank; r += 4) {
+                        const float4 x0 = *reinterpret_cast<const float4 *>(r0 + r), x1 = *reinterpret_cast<const float4 *>(r1 + r);
+                        const float4 x2 = *reinterpret_cast<const float4 *>(r2 + r), x3 = *reinterpret_cast<const float4 *>(r3 + r);
+                        const float w0 = w[r * (dk + 1)], w1 = w[(r + 1) * (dk + 1)], w2v = w[(r + 2) * (dk + 1)], w3 = w[(r + 3) * (dk + 1)];
+                        z[0] = fmaf(w3, x0.w, fmaf(w2v, x0.z, fmaf(w1, x0.y, fmaf(w0, x0.x, z[0]))));
+                        z[1] = fmaf(w3, x1.w, fmaf(w2v, x1.z, fmaf(w1, x1.y, fmaf(w0, x1.x, z[1]))));
+                        z[2] = fmaf(w3, x2.w, fmaf(w2v, x2.z, fmaf(w1, x2.y, fmaf(w0, x2.x, z[2]))));
+                        z[3] = fmaf(w3, x3.w, fmaf(w2v, x3.z, fmaf(w1, x3.y, fmaf(w0, x3.x, z[3]))));
+                    }
+                }
+                for (; r < a.rank; ++r) {
                     const float wv = w[r * (dk + 1)];
                     z[0] = fmaf(wv, r0[r], z[0]);
                     z[1] = fmaf(wv, r1[r], z[1]);
@@ -623,7 +640,7 @@ linear_scan_kernel(ScanArgs a) {
                         sx[(tt0 + j) * dkp + kk].x = a.decay_form == 1 ? expf(-expf(z[j])) : expf(log_sigmoid_f(z[j]) * a.inv_tau);
             }
             __syncthreads();
-        } else if (a.w2 != nullptr) {
+        } else if (PROJ) {
             for (int i = threadIdx.x; i < n * dk; i += SCAN_THREADS) {
                 const int tt = i / dk, kk = i - tt * dk;
                 const TW *w = (const TW *)a.w2 + (size_t)(head * dk + kk) * a.rank;
@@ -890,31 +907,42 @@ JK_EXPORT int jk_linear_scan(const float *u, int ld, int q_off, int k_off, int v
     dim3 grid(heads, items, (dv + cols - 1) / cols);
     JK_REQUIRE(items <= 65535 && grid.z <= 65535 && heads <= 65535, "linear_scan: %d items in one launch", items);
     const size_t smem = row_bytes * chunk + (stage_w2 ? w2_bytes : 0);
-#define SCAN_LAUNCH_C(TW, KS, C)                                                                                                \
+#define SCAN_LAUNCH_O(TW, KS, C, P, O)                                                                                          \
     do {                                                                                                                        \
         if (smem > 48 * 1024)                                                                                                   \
-            cudaFuncSetAttribute(linear_scan_kernel<TW, KS, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-        jk_launch(linear_scan_kernel<TW, KS, C>, grid, dim3(SCAN_THREADS), smem, stream, a);                                    \
+            cudaFuncSetAttribute(linear_scan_kernel<TW, KS, C, P, O>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+        jk_launch(linear_scan_kernel<TW, KS, C, P, O>, grid, dim3(SCAN_THREADS), smem, stream, a);                              \
     } while (0)
-#define SCAN_LAUNCH(TW, KS)                         \
+#define SCAN_LAUNCH_C(TW, KS, C, P)                                         \
+    do {                                                                    \
+        if constexpr (KS * C <= 16) {                                       \
+            if (n_pieces > 0) SCAN_LAUNCH_O(TW, KS, C, P, 3);               \
+            else SCAN_LAUNCH_O(TW, KS, C, P, 2);                            \
+        } else {                                                            \
+            SCAN_LAUNCH_O(TW, KS, C, P, 2);                                 \
+        }                                                                   \
+    } while (0)
+#define SCAN_LAUNCH(TW, KS, P)                      \
     do {                                            \
-        if (cpt == 4) SCAN_LAUNCH_C(TW, KS, 4);     \
-        else SCAN_LAUNCH_C(TW, KS, 2);              \
+        if (cpt == 4) SCAN_LAUNCH_C(TW, KS, 4, P);  \
+        else SCAN_LAUNCH_C(TW, KS, 2, P);           \
     } while (0)
-#define SCAN_LAUNCH_T(TW)                                   \
-    do {                                                    \
-        if (per_thread <= 1) SCAN_LAUNCH(TW, 1);            \
-        else if (per_thread <= 2) SCAN_LAUNCH(TW, 2);       \
-        else if (per_thread <= 4) SCAN_LAUNCH(TW, 4);       \
-        else if (per_thread <= 8) SCAN_LAUNCH(TW, 8);       \
-        else if (per_thread <= 16) SCAN_LAUNCH(TW, 16);     \
-        else if (per_thread <= 32) SCAN_LAUNCH(TW, 32);     \
-        else SCAN_LAUNCH(TW, 64);                           \
+#define SCAN_LAUNCH_T(TW, P)                                   \
+    do {                                                       \
+        if (per_thread <= 1) SCAN_LAUNCH(TW, 1, P);            \
+        else if (per_thread <= 2) SCAN_LAUNCH(TW, 2, P);       \
+        else if (per_thread <= 4) SCAN_LAUNCH(TW, 4, P);       \
+        else if (per_thread <= 8) SCAN_LAUNCH(TW, 8, P);       \
+        else if (per_thread <= 16) SCAN_LAUNCH(TW, 16, P);     \
+        else if (per_thread <= 32) SCAN_LAUNCH(TW, 32, P);     \
+        else SCAN_LAUNCH(TW, 64, P);                           \
     } while (0)
-    if (w2 != nullptr && w2_dtype == JK_BF16)
-        SCAN_LAUNCH_T(__nv_bfloat16);
+    if (w2 == nullptr)
+        SCAN_LAUNCH_T(float, false);
+    else if (w2_dtype == JK_BF16)
+        SCAN_LAUNCH_T(__nv_bfloat16, true);
     else
-        SCAN_LAUNCH_T(float);
+        SCAN_LAUNCH_T(float, true);
     JK_CHECK_LAUNCH("linear_scan");
     if (n_pieces > 0) {
         jk_launch(scan_carry_kernel, dim3((dk * dv + 255) / 256, heads, n_piece_reqs), dim3(256), 0, stream, a);
