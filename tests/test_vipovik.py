@@ -75,8 +75,14 @@ MODELS = {
     # nothing a multiple of anything: odd width, odd sizes everywhere, a prime vocabulary
     "awkward": config(50, 61, [layer(left(3, 3, 10, 7, 0.4, 11.0, 13, 2, 6, 555.0), 3, 5, 3, (0.6, 0.9), moe(2, 1, 11, 1.2)),
                                layer(left(2, 1, 6, 9, 0.5, 5.0, 5, 1, 2), 1, 7, 2, (1.2, 0.4), dense(21))], loop=(0, 1, 3)),
+    # heads of 64 and 128 for keys, values and the recurrence, as the tensor-core attention kernels and the scan's instances for
+    # whole heads take them; prompts longer than a piece of the scan
+    "wide": config(256, 333, [layer(left(4, 2, 64, 64, 0.125, 20.0, 48, 2, 64, 1e4, (4.0, 64, 16.0, 1.0)), 3, 64, 32, (0.6, 0.5), dense(512)),
+                              layer(left(2, 1, 128, 128, 0.09, 25.0, 100, 3, 64), 2, 128, 64, (0.5, 0.7), moe(4, 2, 128, 2.0))],
+                   loop=(1, 2, 2), scale=4.0),
 }
 STD = 0.16     # matrices N(0, STD): products keep their input's spread, so scores, gates and routers are far from flat
+STDS = {"wide": 0.08}       # the same for rows four times as wide
 
 
 @pytest.fixture(scope="module")
@@ -88,7 +94,7 @@ def folders(tmp_path_factory):
     out = {}
     for seed, (name, cfg) in enumerate(MODELS.items()):
         d = str(tmp_path_factory.mktemp("vipovik_" + name))
-        write_model_folder(config_class_for(cfg).from_dict(cfg), d, seed=seed + 51, std=STD, norm_std=0.2)
+        write_model_folder(config_class_for(cfg).from_dict(cfg), d, seed=seed + 51, std=STDS.get(name, STD), norm_std=0.2)
         path = os.path.join(d, "config.json")
         with open(path) as f:
             disk = json.load(f)
