@@ -54,7 +54,7 @@ struct TgArgs {
     int M, N, K, ldo;
     float scale;
     int *status;       // device word: 0, or the code of the wait that ran out
-    int direct;        // 1: the output's rows are not 16-byte aligned, store from registers instead of by TMA
+    int direct;        // 1: the output's rows are not 16-byte aligned or not whole units of 16 bytes: store from registers, not by TMA
     int ksplit;        // EPI_RESIDUAL by TMA only: a tile's K is cut into this many units whose partial products all add
                        // themselves into the output (0 or 1: none)
     QkvDest qkv;       // EPI_QKV only
@@ -518,8 +518,10 @@ JK_EXPORT int jk_gemm_tcgen05(const void *act, const void *w, void *out, int M, 
     CUtensorMap ma, mw, mo;
     if (int rc = tensor_map_2d(act, M, K, K, TG_BM, TG_BK, 2, &ma)) return rc;
     TgArgs a{out, M, N, K, ldo, scale, status, 0, 0, QkvDest{}, gate_act};
-    // the output goes out by TMA when its rows are 16-byte aligned, else straight from registers
-    a.direct = ((size_t)ldo * out_bytes) % 16 != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0;
+    // the output goes out by TMA when its rows are 16-byte aligned and whole units of 16 bytes wide, else straight from
+    // registers: a TMA store clips at the tensor's edge in units of 16 bytes, so a narrower last unit would be written whole,
+    // over the columns beside a product that fills a column range of wider rows
+    a.direct = ((size_t)ldo * out_bytes) % 16 != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0 || ((size_t)N * out_bytes) % 16 != 0;
     if (a.direct) mo = ma;
     else if (int rc = tensor_map_2d(out, M, N, ldo, 32, 128 / out_bytes, out_bytes, &mo)) return rc;
     bool pair = takes_pairs(M, N, epilogue == EPI_SWIGLU ? 128 : 256, sms);

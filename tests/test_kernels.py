@@ -709,6 +709,36 @@ def test_gemm_tcgen05_with_store_and_residual_epilogues(K, pairs, M, N, K_, epi)
         torch.testing.assert_close(out.double().cpu(), x.double() + 0.7 * want, rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("M,K_,widths", [(300, 256, (256, 256, 192, 192, 32)), (200, 96, (40, 24, 7)), (1024, 512, (512, 384, 64)),
+                                         (64, 256, (256, 130, 30))])
+def test_products_into_column_ranges_of_wider_rows(K, pairs, M, K_, widths):
+    """Several products, each from activations of its own, into neighbouring column ranges of the same float32 rows (what a
+    mixer whose projections read different mixtures asks for): every range holds its product, and nothing else is written.
+    Row strides that are and are not multiples of 16 bytes."""
+    g = torch.Generator().manual_seed(M + K_ + sum(widths))
+    for pad in (0, 1):
+        ld = sum(widths) + pad
+        wide = torch.full((M, ld), 9.0, device=DEV)
+        off, wants = 0, []
+        for n in widths:
+            act = torch.randn(M, K_, generator=g).to(torch.bfloat16)
+            w = (torch.randn(n, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+            wants.append(act.double() @ w.double().T)
+            out = wide[:, off: off + n]
+            if M <= 128 and K.gemm_skinny_supports(M, n, K_):
+                K.gemm_skinny(act.to(DEV), w.to(DEV), out, K.TG_F32)
+            else:
+                K.gemm_tcgen05(act.to(DEV), w.to(DEV), out, K.TG_F32)
+            K.check_gemm_status(DEV)
+            off += n
+        got = wide.double().cpu()
+        off = 0
+        for n, want in zip(widths, wants):
+            torch.testing.assert_close(got[:, off: off + n], want, rtol=1e-4, atol=1e-4)
+            off += n
+        assert bool((got[:, off:] == 9.0).all())
+
+
 @pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (300, 136, 96), (2048, 5760, 2304), (77, 520, 200)])
 def test_gemm_tcgen05_with_swiglu_epilogue(K, pairs, M, N, K_):
     g = torch.Generator().manual_seed(M * 3 + N)
