@@ -155,6 +155,8 @@ int bind_from_directory(JkModel *m, const char *dir, bool need_gemm_tcgen05, boo
     f.linear_small_norm_supports = (SupportsFn)sym(ls, "jk_linear_small_norm_supports");
     f.linear_small_norm = (LinearSmallNormFn)sym(ls, "jk_linear_small_norm");
     f.linear_small_qkv_norm = (LinearSmallQkvNormFn)sym(ls, "jk_linear_small_qkv_norm");
+    f.linear_small_parts = (LinearSmallPartsFn)sym(ls, "jk_linear_small_parts");
+    f.linear_small_parts_supports = (SupportsFn)sym(ls, "jk_linear_small_parts_supports");
     g_small_fault = (int (*)())sym(ls, "jk_linear_small_take_fault");
     f.gemm_tcgen05 = (GemmTcgen05Fn)sym(gt, "jk_gemm_tcgen05");
     f.gemm_tcgen05_qkv = (GemmTcgen05QkvFn)sym(gt, "jk_gemm_tcgen05_qkv");

@@ -67,6 +67,12 @@ struct SmallLinearArgs {
     SmallNormFuse norm;         // the tile kernel only
     int *fault;                 // the TMA tile kernel: receives 1 when its bounded wait runs out, 2 for misaligned shared memory
     int gate_act;               // EPI_SWIGLU: JkGateAct of the gate
+    // Several products of one launch (the tile kernel, EPI_F32): features part_end[p - 1] .. part_end[p] - 1 are the product
+    // of the activations act + p * part_stride.  n_parts <= 1: one product.  Every end but the last is a multiple of 16, so
+    // a tile lies in one part.
+    int n_parts;
+    long long part_stride;      // elements
+    int part_end[8];
 };
 
 constexpr int SL_MAX_WARPS = 8;
@@ -377,12 +383,18 @@ small_linear_tile_kernel(const __grid_constant__ CUtensorMap map_w, SmallLinearA
             }
     }
 
+    const __nv_bfloat16 *act_base = a.act;
+    if (EPI == EPI_F32 && a.n_parts > 1) {          // the activations of the part that holds this tile
+        int part = 0;
+        while (part + 1 < a.n_parts && n0 >= a.part_end[part]) ++part;
+        act_base += (size_t)part * (size_t)a.part_stride;
+    }
     const __nv_bfloat16 *ap[MT];
     bool arow[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
         arow[m] = m * 8 + g < a.M;
-        ap[m] = a.act + (size_t)(arow[m] ? m * 8 + g : 0) * a.K + (size_t)kb_begin * 32 + t * 8;
+        ap[m] = act_base + (size_t)(arow[m] ? m * 8 + g : 0) * a.K + (size_t)kb_begin * 32 + t * 8;
     }
     float acc[MT][4];
 #pragma unroll
@@ -788,6 +800,44 @@ static int linear_small_impl(const void *act, const void *w, void *out, int M, i
     if (MT == 1) SL_LAUNCH(1, EPI_SWIGLU);
     SL_LAUNCH(2, EPI_SWIGLU);
 #undef SL_LAUNCH
+}
+
+// Several products of few rows as one launch: out[:, part_end[p - 1] .. part_end[p] - 1] = act_p @ W[those rows]^T with
+// act_p = act + p * part_stride elements ([M, K] each), W [N, K] and float32 out [M, ldo].  What a mixer asks for whose
+// projections read different mixtures of its input.  The tile kernel only: `jk_linear_small_parts_supports` says whether it
+// takes the shape; every part's end but the last must be a multiple of 16.
+static size_t parts_tile_smem(int M, int K, int *ksplit_out) {
+    int ksplit = ST_MAX_WARPS;
+    while (ksplit > 1 && (K / 32) / ksplit < 2) ksplit /= 2;
+    if (ksplit_out) *ksplit_out = ksplit;
+    return small_tile_smem(K, M <= 8 ? 1 : 2, ksplit);
+}
+JK_EXPORT int jk_linear_small_parts_supports(int M, int N, int K) {
+    if (M < 1 || M > 16 || N < 1 || K < 32 || K % 32) return 0;
+    return parts_tile_smem(M, K, nullptr) <= 200 * 1024;
+}
+JK_EXPORT int jk_linear_small_parts(const void *act, long long part_stride, const int *part_end, int n_parts, const void *w,
+                                    void *out, int M, int N, int K, int ldo, int sms, cudaStream_t stream) {
+    JK_REQUIRE(act && part_end && w && out && n_parts >= 1 && n_parts <= 8 && part_stride >= 0, "linear_small_parts: an argument is missing");
+    JK_REQUIRE(jk_linear_small_parts_supports(M, N, K) && ldo >= N, "linear_small_parts: M %d N %d K %d ldo %d", M, N, K, ldo);
+    JK_REQUIRE((part_stride * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(act) & 15) == 0, "linear_small_parts: activations must be 16-byte aligned");
+    if (sms <= 0) sms = 148;
+    // as the single product: 16 warps a tile unless the tiles give every SM two blocks
+    int ksplit = (N + 15) / 16 < 2 * sms ? ST_MAX_WARPS : SL_MAX_WARPS;
+    while (ksplit > 1 && (K / 32) / ksplit < 2) ksplit /= 2;
+    SmallLinearArgs a{(const __nv_bfloat16 *)act, (const __nv_bfloat16 *)w, out, M, N, K, ldo, ksplit, 0, SmallQkvDest{}, SmallNormFuse{}};
+    a.gate_act = 0;
+    a.n_parts = n_parts;
+    a.part_stride = part_stride;
+    int before = 0;
+    for (int p = 0; p < n_parts; ++p) {
+        JK_REQUIRE(part_end[p] > before && (p + 1 == n_parts ? part_end[p] == N : part_end[p] % 16 == 0),
+                   "linear_small_parts: part %d ends at feature %d of %d", p, part_end[p], N);
+        a.part_end[p] = before = part_end[p];
+    }
+    const size_t smem = small_tile_smem(K, M <= 8 ? 1 : 2, ksplit);
+    if (M <= 8) return launch_tile<1, EPI_F32>(a, smem, stream);
+    return launch_tile<2, EPI_F32>(a, smem, stream);
 }
 
 JK_EXPORT int jk_linear_small(const void *act, const void *w, void *out, int M, int N, int K, int ldo,

@@ -401,6 +401,41 @@ int run_linear(Run &r, const RunnerOp &op) {
     return product_f32(r, in, op.w, op.vec, (float *)out, rows, op.n, op.k);
 }
 
+// Steps of few rows: products in a row that read neighbouring parts of one slot (a mixer whose projections each read their
+// own mixture of its input), with neighbouring rows of one weight matrix, into neighbouring column ranges of the same
+// float32 rows, run as one launch of the few-row kernel.  Returns how many records from ops[i] on it ran (0: none; the
+// caller runs them one by one).
+int run_linears_together(Run &r, const RunnerOp *ops, int i, int end, int *ran) {
+    *ran = 0;
+    const RunnerOp &op = ops[i];
+    const int rows = r.st.ntok;
+    if (g_fns.linear_small_parts == nullptr || g_fns.linear_small_parts_supports == nullptr || r.env.dtype != JK_BF16 || rows > 16 || rows == 0 ||
+        op.wanted_rows || op.ld <= 0 || op.in_part != 0 || op.vec != nullptr)
+        return JK_OK;
+    int ends[8], n = 0, width = 0;
+    for (int j = i; j < end && n < 8; ++j) {
+        const RunnerOp &o = ops[j];
+        if (o.kind != OP_LINEAR || o.wanted_rows || o.vec != nullptr || o.in_slot != op.in_slot || o.out_slot != op.out_slot || o.ld != op.ld ||
+            o.k != op.k || o.in_part != n || o.out_off != op.out_off + width ||
+            (const char *)o.w != (const char *)op.w + (size_t)width * op.k * r.elem())
+            break;
+        if (n > 0 && width % 16 != 0) break;        // a tile of 16 features lies in one part
+        width += o.n;
+        ends[n++] = width;
+    }
+    if (n < 2) return JK_OK;
+    while (n >= 2 && r.route(rows, width, op.k, jk::PRODUCT_F32) != jk::ROUTE_SMALL) width = ends[--n - 1];
+    if (n < 2 || !g_fns.linear_small_parts_supports(rows, width, op.k)) return JK_OK;
+    void *in, *out;
+    if (int rc = r.slot(op.in_slot, (long long)r.elem() * rows * op.k * n, &in, "the products' activations")) return rc;
+    if (int rc = r.slot(op.out_slot, 4LL * rows * op.ld, &out, "the products' output")) return rc;
+    JK_REQUIRE(op.out_off >= 0 && op.out_off + width <= op.ld, "runner: products write columns %d .. %d of rows of %d", op.out_off, op.out_off + width, op.ld);
+    RUN(linear_small, g_fns.linear_small_parts(in, (long long)rows * op.k, ends, n, op.w, (float *)out + op.out_off, rows, width, op.k, op.ld,
+                                               r.env.routing.sms, r.stream));
+    *ran = n;
+    return JK_OK;
+}
+
 // ---- records of csrc/mixers.cu -------------------------------------------------------------------------------
 int need_mixers(const char *what) {
     JK_REQUIRE(g_fns.layernorm != nullptr, "runner: %s needs the mixers module, which was not bound", what);
@@ -718,9 +753,13 @@ JK_EXPORT int jk_runner_run(const RunnerEnv *envp, const RunnerOp *ops, int firs
                 fused = FusedNorm{};
                 break;
             }
-            case OP_LINEAR:
-                rc = run_linear(r, op);
+            case OP_LINEAR: {
+                int ran = 0;
+                rc = run_linears_together(r, ops, i, first + count, &ran);
+                if (rc == JK_OK && ran > 0) i += ran - 1;
+                else if (rc == JK_OK) rc = run_linear(r, op);
                 break;
+            }
             case OP_CAST:
                 hidden = op.n;
                 rc = run_cast(r, op);

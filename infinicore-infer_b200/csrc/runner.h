@@ -41,6 +41,7 @@ typedef int (*AttentionTcgen05Fn)(const void *, const void *, const void *, void
                                   const int *, const int *, int, int, int, int, int, int, float, int, int *, int, const float *, int,
                                   float, int, cudaStream_t);
 typedef int (*SupportsFn)(int, int, int);
+typedef int (*LinearSmallPartsFn)(const void *, long long, const int *, int, const void *, void *, int, int, int, int, int, cudaStream_t);
 typedef int (*Supports1Fn)(int);
 typedef int (*LinearSmallNormFn)(const void *, const void *, void *, int, int, int, int, int, const unsigned long long *, float,
                                  void *, const float *, unsigned long long *, float, int *, int, cudaStream_t);
@@ -143,6 +144,9 @@ struct RunnerFns {
     CountFn routed_experts_launches;
     SoftcapFn softcap;
     LastErrorFn err_blocks;
+    // several few-row products of one launch (csrc/linear_small.cu); may be empty: the products then run one by one
+    LinearSmallPartsFn linear_small_parts;
+    SupportsFn linear_small_parts_supports;
 };
 
 // ---- records ---------------------------------------------------------------------------------------------------

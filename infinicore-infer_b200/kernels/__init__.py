@@ -201,6 +201,28 @@ def linear_small(act: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue
     return out
 
 
+def linear_small_parts_supports(m: int, n: int, k: int) -> bool:
+    """Whether the few-row tile kernel takes several products of ``m`` rows over ``k`` with ``n`` features in all as one launch."""
+    return bool(_build.load("linear_small").jk_linear_small_parts_supports(_c_int(m), _c_int(n), _c_int(k)))
+
+
+def linear_small_parts(acts: torch.Tensor, w: torch.Tensor, ends, out: torch.Tensor) -> torch.Tensor:
+    """Several products of at most 16 rows in one launch: ``out[:, ends[p-1]:ends[p]] = acts[p] @ w[ends[p-1]:ends[p]]^T`` for
+    bfloat16 ``acts`` [parts, M, K] and ``w`` [N, K], float32 ``out`` [M, N] (rows may be wider: its stride is taken).  Every end
+    but the last is a multiple of 16."""
+    _need(acts, "acts", torch.bfloat16); _need(w, "w", torch.bfloat16)
+    _need(out, "out", torch.float32, contiguous=False)
+    parts, m, k = acts.shape
+    n = w.shape[0]
+    if w.shape[1] != k or tuple(out.shape) != (m, n) or out.stride(1) != 1 or len(ends) != parts or parts > 8:
+        raise KernelError(f"linear_small_parts: acts {tuple(acts.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, ends {list(ends)}")
+    lib = _build.load("linear_small")
+    arr = (ctypes.c_int * parts)(*[int(e) for e in ends])
+    _check("linear_small", lib.jk_linear_small_parts(_ptr(acts), ctypes.c_longlong(m * k), arr, _c_int(parts), _ptr(w), _ptr(out), _c_int(m),
+                                                     _c_int(n), _c_int(k), _c_int(out.stride(0)), _c_int(_sm_count(acts.device)), _stream()))
+    return out
+
+
 def linear_small_qkv_supports(m: int, k: int, dh: int) -> bool:
     """Whether the small-row product can take the fused [q | k | v] projection with rotation and cache
     write in its epilogue."""

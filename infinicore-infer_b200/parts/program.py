@@ -91,7 +91,7 @@ class _Fns(ctypes.Structure):
         "linear_small_qkv_norm", "argmax", "sample", "err_sampling", "layernorm", "cast_rows", "glu", "conv_qkv", "linear_scan",
         "norm_gate", "token_shift", "act_rows", "err_mixers", "norm_add", "concat_cast", "add_bias_rows", "latent_qkv", "head_linear", "latent_attention",
         "latent_attention_scratch", "causal_conv", "selective_scan", "routed_experts", "routed_experts_workspace",
-        "routed_experts_launches", "softcap", "err_blocks")]
+        "routed_experts_launches", "softcap", "err_blocks", "linear_small_parts", "linear_small_parts_supports")]
 
 
 def _addr(lib, name: str) -> int:
@@ -148,7 +148,9 @@ def runner_lib(gemm_tcgen05: bool = False, attention_tcgen05: bool = False, mixe
         causal_conv=get("blocks", "jk_causal_conv"), selective_scan=get("blocks", "jk_selective_scan"),
         routed_experts=get("blocks", "jk_routed_experts"), routed_experts_workspace=get("blocks", "jk_routed_experts_workspace"),
         routed_experts_launches=get("blocks", "jk_routed_experts_launches"), softcap=get("blocks", "jk_softcap"),
-        err_blocks=get("blocks", "jk_blocks_last_error"))
+        err_blocks=get("blocks", "jk_blocks_last_error"),
+        linear_small_parts=get("linear_small", "jk_linear_small_parts"),
+        linear_small_parts_supports=get("linear_small", "jk_linear_small_parts_supports"))
     if lib.jk_runner_bind(ctypes.byref(fns)):
         from ..kernels import KernelError
         raise KernelError(lib.jk_runner_last_error().decode(errors="replace"))

@@ -709,6 +709,26 @@ def test_gemm_tcgen05_with_store_and_residual_epilogues(K, pairs, M, N, K_, epi)
         torch.testing.assert_close(out.double().cpu(), x.double() + 0.7 * want, rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("M,K_,widths", [(1, 64, (48, 48, 32, 32, 5)), (8, 2048, (256, 256, 256, 256, 64)), (13, 320, (192, 64, 7)), (16, 96, (16, 16))])
+def test_few_row_products_of_different_activations_in_one_launch(K, M, K_, widths):
+    """Each column range is the product of ITS activations (not of a neighbour's) with its rows of the matrix; columns
+    beside the ranges stay as they were."""
+    g = torch.Generator().manual_seed(M + K_ + len(widths))
+    N = sum(widths)
+    assert K.linear_small_parts_supports(M, N, K_)
+    acts = torch.randn(len(widths), M, K_, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16)
+    ends = [sum(widths[:i + 1]) for i in range(len(widths))]
+    wide = torch.full((M, N + 3), 9.0, device=DEV)
+    K.linear_small_parts(acts.to(DEV), w.to(DEV), ends, wide[:, 1: 1 + N])
+    got = wide.double().cpu()
+    lo = 0
+    for p, hi in enumerate(ends):
+        torch.testing.assert_close(got[:, 1 + lo: 1 + hi], acts[p].double() @ w[lo:hi].double().T, rtol=1e-4, atol=1e-4)
+        lo = hi
+    assert bool((got[:, 0] == 9.0).all()) and bool((got[:, 1 + N:] == 9.0).all())
+
+
 @pytest.mark.parametrize("M,K_,widths", [(300, 256, (256, 256, 192, 192, 32)), (200, 96, (40, 24, 7)), (1024, 512, (512, 384, 64)),
                                          (64, 256, (256, 130, 30))])
 def test_products_into_column_ranges_of_wider_rows(K, pairs, M, K_, widths):
