@@ -1,11 +1,12 @@
 """Configuration: typed specifications, the MiniCPM/FM9G config, the architecture registry."""
 from .specs import (AttentionSpec, BlockSpec, ConfigError, ConvAttentionSpec, FrequencyRampSpec, GLUSpec, LatentAttentionSpec,
-                    LayerNormSpec, LinearAttentionSpec, MLPSpec, ModelSpec, PairRotarySpec, ParallelMixerSpec, PostNormBlockSpec, ReinjectSpec, RMSNormSpec,
+                    DeltaRuleSpec, StepVectorSpec, LayerNormSpec, LinearAttentionSpec, MLPSpec, ModelSpec, PairRotarySpec, ParallelMixerSpec, PostNormBlockSpec, ReinjectSpec, RMSNormSpec,
                     RopeSpec, RoutedExpertsSpec, RunEntry, SandwichBlockSpec, SelectiveScanSpec, SwiGLUSpec, default_order)
 from .minicpm import MiniCPMConfig
 from .sitelorn import SitelornConfig
 from .vunelix import VunelixConfig
 from .vipovik import VipovikConfig
+from .fapenex import FapenexConfig
 from .presets import PRESETS, Preset
 from .registry import (architecture_names, config_class_for, read_config,
                        register_architecture)
@@ -17,8 +18,10 @@ for _name in ("minicpm", "fm9g", "llama", "MiniCPMForCausalLM", "LlamaForCausalL
 register_architecture("sitelorn", SitelornConfig)
 register_architecture("vunelix", VunelixConfig)
 register_architecture("vipovik", VipovikConfig)
+register_architecture("fapenex", FapenexConfig)
 
 __all__ = [
+    "DeltaRuleSpec", "StepVectorSpec", "FapenexConfig",
     "MLPSpec", "ParallelMixerSpec", "VipovikConfig",
     "FrequencyRampSpec", "LatentAttentionSpec", "ReinjectSpec", "RoutedExpertsSpec", "SandwichBlockSpec", "SelectiveScanSpec", "VunelixConfig",
     "ConvAttentionSpec", "GLUSpec", "LayerNormSpec", "LinearAttentionSpec", "PairRotarySpec", "PostNormBlockSpec", "SitelornConfig",

@@ -22,10 +22,11 @@ class ConfigError(ValueError):
 @dataclass(frozen=True)
 class RMSNormSpec:
     """y = x * w / sqrt(mean(x^2) + eps)  (reference: src/models/jiuge/jiuge.cpp:198).  ``weight_name`` is appended to the
-    part's prefix."""
+    part's prefix.  ``one_plus``: the checkpoint stores the weight around zero and the norm multiplies by 1 + w."""
     size: int
     eps: float
     weight_name: str = "weight"
+    one_plus: bool = False
     kind: str = "rmsnorm"
 
 
@@ -132,7 +133,12 @@ class ConvAttentionSpec:
     first ``keep_first`` positions visible for good, a sink (a key of score 0 without a value in every softmax), one output gate per
     head (sigmoid of a projection of the mixer's input), and ``shares_kv``: the layer makes queries only and reads the
     keys and values that another layer wrote into its cache.  The names are those of the checkpoint's tensors below the
-    mixer's prefix: projection ``q``, its convolution ``q`` + ``conv_suffix``, its norm ``q`` + ``norm_suffix``."""
+    mixer's prefix: projection ``q``, its convolution ``q`` + ``conv_suffix``, its norm ``q`` + ``norm_suffix``.
+
+    Further options: ``bias``: q, k and v have biases (``q`` + ``bias_suffix``), added in the projection; ``head_norm``
+    "before_rotation": every head of q and k passes an RMS norm BEFORE the rotation, with one weight of ``head_dim`` per
+    projection shared by its heads (``q`` + ``norm_suffix``), eps ``qk_norm_eps``; ``chunk`` C (instead of a window): a query
+    at position i sees the keys j <= i with floor(j / C) = floor(i / C), chunks counted from position 0 of the sequence."""
     hidden_size: int
     num_heads: int
     num_kv_heads: int
@@ -147,7 +153,7 @@ class ConvAttentionSpec:
     sink: bool = False
     head_gate: bool = False
     shares_kv: bool = False
-    head_norm: bool = False
+    head_norm: object = False          # False, True (after the rotation, no weight) or "before_rotation" (weights of head_dim)
     score_cap: float = 0.0
     keep_first: int = 0
     q_name: str = "q"
@@ -157,6 +163,9 @@ class ConvAttentionSpec:
     o_name: str = "o"
     conv_suffix: str = ".conv"
     norm_suffix: str = ".norm"
+    bias: bool = False
+    bias_suffix: str = ".b"
+    chunk: Optional[int] = None
     kind: str = "conv_attention"
 
 
@@ -219,7 +228,11 @@ class LatentAttentionSpec:
     ``rot_dim`` more that are rotated and serve every head as the rotated part of its key.  Head h's plain key is
     ``k_up_name``[h] c, its value ``v_up_name``[h] c (``v_head_dim`` elements); score = (q_plain . k_plain + q_rot . k_rot) *
     ``softmax_scale``.  The cache holds c and the rotated part only.  ``output_gate``: the heads' outputs side by side are
-    multiplied by sigmoid(``gate_name`` h) before the output product."""
+    multiplied by sigmoid(``gate_name`` h) before the output product.
+
+    ``q_rank`` > 0: the queries go through a latent of their own, c_q = RMSnorm(``q_down_name`` h) with the weight
+    ``q_down_name`` + ``norm_suffix``, q = ``q_up_name`` c_q.  ``window`` W: a query at position i sees the keys j with
+    0 <= i - j < W.  ``rot_dim`` may be 0 (no rotated part)."""
     hidden_size: int
     num_heads: int
     head_dim: int
@@ -230,6 +243,10 @@ class LatentAttentionSpec:
     norm_eps: float
     position: Optional[PairRotarySpec] = None
     output_gate: bool = True
+    window: Optional[int] = None
+    q_rank: int = 0
+    q_down_name: str = "dq"
+    q_up_name: str = "uq"
     q_name: str = "q"
     kv_down_name: str = "dkv"
     k_up_name: str = "uk"
@@ -270,8 +287,11 @@ class RoutedExpertsSpec:
     without renormalising.  ``shared``: a gated unit that every row passes, added on top.
 
     ``score_form`` "softmax_renorm": scores are softmax(router h) over all experts, the chosen ones' scores are divided by
-    their sum (+ 1e-20) and multiply the units' OUTPUTS (``scale_input`` False).  ``act`` "swish_clamp": a unit's inner value
-    is g' sigmoid(1.702 g') (u' + 1) with g' = min(gate h, limit), u' = clamp(up h, -limit, limit)."""
+    their sum (+ 1e-20) and multiply the units' OUTPUTS (``scale_input`` False); that is the softmax over the chosen
+    logits alone.  ``act`` "swish_clamp": a unit's inner value is g' sigmoid(1.702 g') (u' + 1) with g' = min(gate h, limit),
+    u' = clamp(up h, -limit, limit).  ``router_bias``: the logits are router h + ``router_name`` + ``bias_suffix``.
+    ``shared_gate_name``: the shared unit's output is multiplied by sigmoid(w . h), one number per row, w that tensor
+    ([1, hidden], below ``shared_prefix``)."""
     hidden_size: int
     num_experts: int
     top: int
@@ -282,6 +302,9 @@ class RoutedExpertsSpec:
     score_form: str = "sigmoid"
     limit: float = 0.0
     router_name: str = "router"
+    router_bias: bool = False
+    bias_suffix: str = ".b"
+    shared_gate_name: Optional[str] = None
     expert_prefix: str = "e{}."
     shared_prefix: str = "shared."
     gate_name: str = "gate"
@@ -300,6 +323,56 @@ class ReinjectSpec:
     weight_name: str = "loop.in"
     step_name: Optional[str] = "loop.step"
     kind: str = "reinject"
+
+
+@dataclass(frozen=True)
+class StepVectorSpec:
+    """A step between two layers that adds one row of a table to every row of the stream: x <- x + ``table_name``[``index``]
+    (the table [``steps``, hidden]; a vector per pass of a repeated span, say)."""
+    hidden_size: int
+    steps: int
+    index: int
+    table_name: str = "loop.step"
+    kind: str = "step_vector"
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """The gated delta rule, a recurrence per head with the state S [head_dim, v_head_dim] in float32 per request:
+
+        S <- g_t S;   w_t = beta_t (v_t - S^T k_t);   S <- S + k_t w_t^T;   o_t = S^T q_t
+
+    q and k have ``num_kv_heads`` heads of ``head_dim`` (query head h uses head h // (num_heads / num_kv_heads)), v has
+    ``num_heads`` heads of ``v_head_dim``; none has a bias.  Each passes a causal convolution over time per channel
+    (``conv_taps`` taps, tensor ``q`` + ``conv_suffix`` [channels, taps], the last column the current row's, zeros before
+    the sequence) and ``conv_act``; q and k then become unit vectors per head, x / sqrt(sum(x^2) + ``unit_eps``), q also
+    times ``q_scale`` (None: head_dim ** -0.5).  beta_t = sigmoid(``beta_name`` h) and g_t = exp(-exp(``a_log_name``)
+    softplus(``decay_name`` h + ``dt_bias_name``)), one each per head.  The heads' outputs are divided by their root mean
+    square over v_head_dim (``norm_eps``), times the weight ``norm_name`` [v_head_dim] shared by the heads, times
+    ``gate_act`` of ``gate_name`` h, and projected by ``o_name``.  The convolutions' last taps - 1 inputs are state too."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    conv_taps: int
+    norm_eps: float
+    unit_eps: float = 1e-6
+    q_scale: Optional[float] = None
+    conv_act: str = "silu"
+    gate_act: str = "silu"
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    beta_name: str = "b"
+    decay_name: str = "a"
+    a_log_name: str = "A_log"
+    dt_bias_name: str = "dt_bias"
+    gate_name: str = "g"
+    norm_name: str = "norm"
+    o_name: str = "o"
+    conv_suffix: str = ".conv"
+    kind: str = "delta_rule"
 
 
 @dataclass(frozen=True)
@@ -323,10 +396,12 @@ class SandwichBlockSpec:
 
 @dataclass(frozen=True)
 class GLUSpec:
-    """down(act(gate(x)) * up(x)) with ``act`` "silu", "relu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
+    """down(act(gate(x)) * up(x)) with ``act`` "silu", "relu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))),
+    or "swish_clamp": down(g' sigmoid(1.702 g') (u' + 1)) with g' = min(gate x, limit), u' = clamp(up x, -limit, limit)."""
     hidden_size: int
     intermediate_size: int
     act: str = "gelu_tanh"
+    limit: float = 0.0
     gate_name: str = "gate"
     up_name: str = "up"
     down_name: str = "down"
@@ -419,6 +494,8 @@ class ModelSpec:
     embed_scale: float = 1.0
     logit_scale: float = 1.0
     logit_softcap: float = 0.0         # c > 0: logits <- c tanh(logits / c)
+    position_table_name: Optional[str] = None      # a learned vector per position [position_rows, hidden], added to the embedding
+    position_rows: int = 0
     tie_embeddings: bool = False
     embed_name: str = "model.embed_tokens.weight"
     lm_head_name: str = "lm_head.weight"

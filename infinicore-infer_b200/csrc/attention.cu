@@ -2,7 +2,8 @@
 //
 // One contract for every way of cutting the work: a step holds rows; row t is a query at
 // absolute position positions[t] of request row_req[t]; its keys are the cache entries of
-// that request at positions lo..positions[t], lo = 0 or positions[t] - window + 1.  Keys and
+// that request at positions lo..positions[t], lo = 0, positions[t] - window + 1, or (window < 0: chunks of -window
+// positions) the first position of the query's chunk (jk_mask_lo).  Keys and
 // values of the step's own rows were written to the pages before this kernel runs, so a
 // portion of a prompt, a single decoded token and a whole prompt are the same case.
 // Pages: [num_pages, nkvh, page_size, dh]; block_table[r, b] is the page of request r that
@@ -62,7 +63,7 @@ attention_row_kernel(AttnArgs a) {
     const int hk = h / (a.nh / a.nkvh);
     const int pos = a.positions[t];
     const int *bt = a.block_table + (size_t)a.row_req[t] * a.max_blocks;
-    const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+    const int lo = jk_mask_lo(pos, a.window);
 
     float *qs = q_smem + warp * dh;
     const T *qrow = (const T *)a.q + ((size_t)t * a.nh + h) * dh;
@@ -140,7 +141,6 @@ static int check_args(const AttnArgs &a) {
                a.T, a.nh, a.nkvh, a.dh);
     JK_REQUIRE(a.nh % a.nkvh == 0, "attention: %d query heads are no multiple of %d key heads", a.nh, a.nkvh);
     JK_REQUIRE(a.page_size > 0 && a.max_blocks > 0, "attention: page size %d, blocks %d", a.page_size, a.max_blocks);
-    JK_REQUIRE(a.window >= 0, "attention: window %d", a.window);
     return JK_OK;
 }
 
@@ -238,7 +238,7 @@ __device__ __forceinline__ float cap_tanh(float s, float cap, float inv_cap) {
 struct KeyRange {
     int lo, first;                 // the window's first key; the range's first number
     __device__ __forceinline__ KeyRange(int pos, int window, int keep_first) {
-        lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        lo = jk_mask_lo(pos, window);
         first = lo - min(keep_first, lo);
     }
     __device__ __forceinline__ int position(int v) const { return v >= lo ? v : v - first; }
@@ -522,7 +522,7 @@ JK_EXPORT int jk_attention_decode(const void *q, const void *k_pages, const void
     JK_REQUIRE(cap >= 0.f && keep_first >= 0, "attention_decode: cap %g, %d kept keys", cap, keep_first);
     JK_REQUIRE(nrows > 0 && nh > 0 && nkvh > 0 && nh % nkvh == 0, "attention_decode: rows %d heads %d/%d", nrows, nh, nkvh);
     JK_REQUIRE(dh % 8 == 0 && dh >= 8 && dh <= 256, "attention_decode: head size %d (takes multiples of 8 up to 256)", dh);
-    JK_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "attention_decode: page size %d, blocks %d, window %d",
+    JK_REQUIRE(page_size > 0 && max_blocks > 0, "attention_decode: page size %d, blocks %d, window %d",
                page_size, max_blocks, window);
     JK_REQUIRE(splits >= 1 && splits <= 256, "attention_decode: %d splits", splits);
     JK_REQUIRE(splits == 1 || scratch != nullptr, "attention_decode: %d splits need scratch memory", splits);
@@ -634,7 +634,7 @@ attention_prefill_kernel(PrefillArgs a) {
     const int nrows = min(PF_BM, a.req_start[r + 1] - row0);
     const int p0 = a.req_pos[r] + (row0 - a.req_start[r]);   // position of the tile's first row
     const int p_last = p0 + nrows - 1;
-    const int lo = (a.window > 0 && p0 - a.window + 1 > 0) ? p0 - a.window + 1 : 0;
+    const int lo = jk_mask_lo(p0, a.window);
     const int *bt = a.block_table + (size_t)r * a.max_blocks;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t page_stride = (size_t)a.nkvh * a.page_size * DH;
@@ -681,7 +681,7 @@ attention_prefill_kernel(PrefillArgs a) {
 
     const int row_a = warp * 16 + (lane >> 2), row_b = row_a + 8;
     const int pos_a = p0 + min(row_a, nrows - 1), pos_b = p0 + min(row_b, nrows - 1);
-    const int lo_a = a.window > 0 ? pos_a - a.window + 1 : 0, lo_b = a.window > 0 ? pos_b - a.window + 1 : 0;
+    const int lo_a = jk_mask_lo(pos_a, a.window), lo_b = jk_mask_lo(pos_b, a.window);
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
     float o[DH / 8][4];
 #pragma unroll
@@ -715,7 +715,7 @@ attention_prefill_kernel(PrefillArgs a) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) s[i][c] = cap_tanh(s[i][c], a.cap_raw, inv_cap);
         }
-        const bool all_visible = it >= n_kept && (kv0 + BN - 1 <= p0) && (a.window == 0 || kv0 >= p_last - a.window + 1);
+        const bool all_visible = it >= n_kept && (kv0 + BN - 1 <= p0) && kv0 >= jk_mask_lo(p_last, a.window);
         float mx_a = -INFINITY, mx_b = -INFINITY;
         if (!all_visible) {
 #pragma unroll
@@ -1194,7 +1194,7 @@ JK_EXPORT int jk_attention_prefill(const void *q, const void *k_pages, const voi
     JK_REQUIRE(ntiles > 0 && nh > 0 && nkvh > 0 && nh % nkvh == 0, "attention_prefill: tiles %d heads %d/%d", ntiles, nh, nkvh);
     JK_REQUIRE(gate == nullptr || gate_ld >= nh, "attention_prefill: a gate row of %d holds no %d heads", gate_ld, nh);
     JK_REQUIRE(ntiles * (tile_rows / PF_BM) <= 65535, "attention_prefill: %d tiles exceed one launch", ntiles);
-    JK_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "attention_prefill: page size %d, blocks %d, window %d",
+    JK_REQUIRE(page_size > 0 && max_blocks > 0, "attention_prefill: page size %d, blocks %d, window %d",
                page_size, max_blocks, window);
     PrefillArgs a{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_pages, (const __nv_bfloat16 *)v_pages,
                   (__nv_bfloat16 *)out, tiles, req_start, req_pos, block_table,

@@ -268,7 +268,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int nrows = min(AT_BM, a.req_start[r + 1] - row0);
     const int p0 = a.req_pos[r] + (row0 - a.req_start[r]);    // position of the tile's first row
     const int p_last = p0 + nrows - 1;
-    const int lo = (a.window > 0 && p0 - a.window + 1 > 0) ? p0 - a.window + 1 : 0;
+    const int lo = jk_mask_lo(p0, a.window);
     // key tiles this query tile sees: those that hold kept first keys and lie before the window's first tile, then the
     // window's
     const int kv_first = lo / AT_BN * AT_BN;
@@ -376,7 +376,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int row = quarter * 32 + lane;                   // row of the tile
         const int pos = p0 + min(row, nrows - 1);              // rows beyond the request repeat its last row
-        const int lo_row = a.window > 0 ? pos - a.window + 1 : 0;
+        const int lo_row = jk_mask_lo(pos, a.window);
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
         const unsigned tmem_sh = tmem_s + lane_addr + half * AT_HALF;     // this thread's scores
         const unsigned tmem_oh = tmem_o + lane_addr + half * DH;          // this half's accumulator
@@ -386,7 +386,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const int kv0 = tile_at(i) + half * AT_HALF;                 // first key of this thread's part
             if (!__all_sync(0xffffffffu, mbar_wait(&s.s_full, i & 1))) { alive = false; break; }
             tc_fence_after();
-            const bool all_visible = i >= n_kept && (kv0 + AT_HALF - 1 <= p0) && (a.window == 0 || kv0 >= p_last - a.window + 1);
+            const bool all_visible = i >= n_kept && (kv0 + AT_HALF - 1 <= p0) && kv0 >= jk_mask_lo(p_last, a.window);
             unsigned sv[AT_HALF];
 #pragma unroll
             for (int c = 0; c < AT_HALF / 32; ++c) tmem_ld32_issue(tmem_sh + c * 32, sv + c * 32);
@@ -612,7 +612,7 @@ JK_EXPORT int jk_attention_tcgen05(const void *q, const void *k_pages, const voi
     JK_REQUIRE(gate == nullptr || gate_ld >= nh, "attention_tcgen05: a gate row of %d holds no %d heads", gate_ld, nh);
     JK_REQUIRE(jk_attention_tcgen05_supports(dh, page_size), "attention_tcgen05: head size %d with pages of %d is not built", dh, page_size);
     JK_REQUIRE(ntiles > 0 && nh > 0 && nkvh > 0 && nh % nkvh == 0 && ntiles <= 65535, "attention_tcgen05: tiles %d heads %d/%d", ntiles, nh, nkvh);
-    JK_REQUIRE(max_blocks > 0 && window >= 0 && status != nullptr && num_pages > 0, "attention_tcgen05: bad arguments");
+    JK_REQUIRE(max_blocks > 0 && status != nullptr && num_pages > 0, "attention_tcgen05: bad arguments");
     CUtensorMap mq, mk, mv;
     if (int rc = tensor_map(q, ntok, nh * dh, AT_BM, &mq)) return rc;
     if (int rc = tensor_map(k_pages, (long long)num_pages * nkvh * page_size, dh, page_size, &mk)) return rc;

@@ -209,6 +209,8 @@ struct LatentQkvArgs {
     const int *positions, *row_req, *block_table;
     int max_blocks, page_size;
     void *q_plain, *q_full, *pages;
+    const float *q_norm_w;      // with it: q_plain [T, q_rank] = rmsnorm(u[q_off .. q_off + q_rank)) * q_norm_w, the queries' own latent
+    int q_rank;                 // vector (the heads' queries are then a product of it, made by the records that follow)
 };
 
 template <typename T>
@@ -231,6 +233,17 @@ __global__ void latent_qkv_kernel(LatentQkvArgs a) {
     const int page = a.block_table[(size_t)a.row_req[t] * a.max_blocks + pos / a.page_size];
     T *crow = (T *)a.pages + ((size_t)page * a.page_size + (size_t)(pos % a.page_size)) * D;
     for (int e = threadIdx.x; e < a.R; e += blockDim.x) crow[e] = from_f32<T>(u[a.kv_off + e] * inv * a.norm_w[e]);
+    if (a.q_norm_w != nullptr) {
+        float sq = 0.f;
+        for (int e = threadIdx.x; e < a.q_rank; e += blockDim.x) {
+            const float v = u[a.q_off + e];
+            sq += v * v;
+        }
+        const float inv_q = 1.f / sqrtf(block_sum(sq, scratch) / (float)a.q_rank + a.eps);
+        for (int e = threadIdx.x; e < a.q_rank; e += blockDim.x)
+            ((T *)a.q_plain)[(size_t)t * a.q_rank + e] = from_f32<T>(u[a.q_off + e] * inv_q * a.q_norm_w[e]);
+        return;
+    }
     // rotated parts: the shared key part (head index H) and every head's query part
     for (int idx = threadIdx.x; idx < (a.H + 1) * a.dr; idx += blockDim.x) {
         const int h = idx / a.dr, e = idx % a.dr;
@@ -255,14 +268,15 @@ __global__ void latent_qkv_kernel(LatentQkvArgs a) {
 JK_EXPORT int jk_latent_qkv(const float *u, int ld, int q_off, int kv_off, int H, int dn, int dr, int R, int rot_dims, const float *freq,
                             float mag, const float *norm_w, float eps, const int *positions, const int *row_req, const int *block_table,
                             int max_blocks, int page_size, void *q_plain, void *q_full, void *pages, int dtype, int T,
-                            cudaStream_t stream) {
+                            const float *q_norm_w, int q_rank, cudaStream_t stream) {
     if (T == 0) return JK_OK;
-    JK_REQUIRE(u && norm_w && positions && row_req && block_table && q_plain && q_full && pages, "latent_qkv: an argument is missing");
+    JK_REQUIRE(u && norm_w && positions && row_req && block_table && q_plain && (q_full || q_norm_w) && pages, "latent_qkv: an argument is missing");
+    JK_REQUIRE(q_norm_w == nullptr || (q_rank > 0 && dr == 0), "latent_qkv: queries through a latent of %d elements beside a rotated part of %d", q_rank, dr);
     JK_REQUIRE(H > 0 && dn >= 0 && dr >= 0 && R > 0 && page_size > 0, "latent_qkv: heads %d, sizes %d + %d, latent %d", H, dn, dr, R);
     JK_REQUIRE(rot_dims >= 0 && rot_dims <= dr && rot_dims % 2 == 0 && (rot_dims == 0 || freq), "latent_qkv: rotation of %d of %d elements", rot_dims, dr);
     LatentQkvArgs a{u, ld, q_off, kv_off, H, dn, dr, R, rot_dims, freq, mag, eps, norm_w, positions, row_req, block_table,
-                    max_blocks, page_size, q_plain, q_full, pages};
-    const int work = H * (dn + dr);
+                    max_blocks, page_size, q_plain, q_full, pages, q_norm_w, q_rank};
+    const int work = q_norm_w ? std::max(q_rank, R) : H * (dn + dr);
     const int threads = work >= 2048 ? 512 : (work >= 512 ? 256 : 128);
 #define LAUNCH(TT) jk_launch(latent_qkv_kernel<TT>, dim3(T), dim3(threads), 0, stream, a)
     BLOCKS_BY_DTYPE(dtype, "latent_qkv", LAUNCH);
@@ -540,6 +554,7 @@ struct LatentAttnArgs {
     const int *positions, *row_req, *block_table;
     int T, H, R, dr, page_size, max_blocks, splits;
     float scale;
+    int window;             // the mask as one number (jk_mask_lo): 0 every earlier key, W > 0 the last W keys
 };
 
 template <typename T, int NS>
@@ -556,10 +571,10 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(LatentA
     const bool active = h < a.H;
     const int pos = a.positions[t];
     const int *bt = a.block_table + (size_t)a.row_req[t] * a.max_blocks;
-    int lo = 0, hi = pos + 1;
+    int lo = jk_mask_lo(pos, a.window), hi = pos + 1;
     if (a.splits > 1) {
-        const int chunk = (((pos + a.splits) / a.splits) + 31) / 32 * 32;
-        lo = blockIdx.z * chunk;
+        const int chunk = (((hi - lo + a.splits - 1) / a.splits) + 31) / 32 * 32;
+        lo += blockIdx.z * chunk;
         hi = min(pos + 1, lo + chunk);
     }
     if (active) {
@@ -701,6 +716,7 @@ struct LatentTcArgs {
     int nreq, H, R, dr, page_size, max_blocks, splits, HT, RT, ldk;
     float scale;
     int buffers;        // 2: the tile after the one at work is on its way; 1: where two would leave an SM room for one block only
+    int window;         // the mask as one number (jk_mask_lo)
 };
 
 __device__ __forceinline__ void ldmatrix_x2(unsigned &r0, unsigned &r1, const void *smem_row) {
@@ -764,10 +780,10 @@ __global__ void __launch_bounds__(256) latent_attention_tc_kernel(LatentTcArgs a
         }
     }
     const int max_pos = a.positions[t0 + nrows - 1];
-    int lo = 0, hi = max_pos + 1;
+    int lo = jk_mask_lo(a.positions[t0], a.window), hi = max_pos + 1;       // positions rise along a request's rows
     if (a.splits > 1) {
-        const int chunk = (((max_pos + a.splits) / a.splits) + 31) / 32 * 32;
-        lo = blockIdx.z * chunk;
+        const int chunk = (((hi - lo + a.splits - 1) / a.splits) + 31) / 32 * 32;
+        lo += blockIdx.z * chunk;
         hi = min(max_pos + 1, lo + chunk);
     }
     // this thread's two rows of its warp's 16 pairs
@@ -775,6 +791,7 @@ __global__ void __launch_bounds__(256) latent_attention_tc_kernel(LatentTcArgs a
     const int ra = pa / a.HT, rb = pb / a.HT, ha = h0 + pa % a.HT, hb = h0 + pb % a.HT;
     const bool va = ra < nrows && ha < a.H, vb = rb < nrows && hb < a.H;
     const int pos_a = va ? a.positions[t0 + ra] : -1, pos_b = vb ? a.positions[t0 + rb] : -1;
+    const int lo_a = jk_mask_lo(pos_a, a.window), lo_b = jk_mask_lo(pos_b, a.window);
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
     float o[NT][4];
 #pragma unroll
@@ -856,8 +873,8 @@ __global__ void __launch_bounds__(256) latent_attention_tc_kernel(LatentTcArgs a
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const int k = nw * 8 + (lane & 3) * 2 + c, j = j0 + k;
-                row_a[k] = (k < n && j <= pos_a) ? s[c] * a.scale : -INFINITY;
-                row_b[k] = (k < n && j <= pos_b) ? s[2 + c] * a.scale : -INFINITY;
+                row_a[k] = (k < n && j <= pos_a && j >= lo_a) ? s[c] * a.scale : -INFINITY;
+                row_b[k] = (k < n && j <= pos_b && j >= lo_b) ? s[2 + c] * a.scale : -INFINITY;
             }
         }
         __syncthreads();
@@ -950,8 +967,9 @@ JK_EXPORT long long jk_latent_attention_scratch(int T, int H, int R, int splits)
 // `req_start` [nreq + 1] (may be null): with it, bfloat16 rows go to the tensor-core kernel (latent sizes up to 512).
 JK_EXPORT int jk_latent_attention(const void *q, const void *pages, void *out, float *part, int dtype, const int *positions,
                                   const int *row_req, const int *block_table, int max_blocks, int page_size, int T, int H, int R,
-                                  int dr, float scale, int splits, const int *req_start, int nreq, cudaStream_t stream) {
+                                  int dr, float scale, int splits, const int *req_start, int nreq, int window, cudaStream_t stream) {
     if (T == 0) return JK_OK;
+    JK_REQUIRE(window >= 0, "latent_attention: window %d", window);
     JK_REQUIRE(q && pages && out && positions && row_req && block_table, "latent_attention: an argument is missing");
     JK_REQUIRE(H > 0 && R > 0 && dr >= 0 && page_size > 0 && max_blocks > 0, "latent_attention: heads %d, latent %d + %d", H, R, dr);
     JK_REQUIRE(R <= 1024, "latent_attention: a latent size of %d exceeds 1024", R);
@@ -974,7 +992,7 @@ JK_EXPORT int jk_latent_attention(const void *q, const void *pages, void *out, f
         const bool second_block_fits = fixed + 2 * tile > 112 * 1024 && fixed + tile <= 112 * 1024;
         const int buffers = (second_block_fits && (long long)((T + RT - 1) / RT) * grid.y * grid.z > sms) ? 1 : 2;
         LatentTcArgs ta{(const __nv_bfloat16 *)q, (const __nv_bfloat16 *)pages, (__nv_bfloat16 *)out, part, positions, req_start, block_table,
-                        nreq, H, R, dr, page_size, max_blocks, splits, HT, RT, ldk, scale, buffers};
+                        nreq, H, R, dr, page_size, max_blocks, splits, HT, RT, ldk, scale, buffers, window};
         const size_t smem_tc = fixed + buffers * tile;
         JK_REQUIRE(grid.y <= 65535, "latent_attention: %d heads", H);
 #define LAUNCH_TC(NT_)                                                                                                                       \
@@ -992,7 +1010,7 @@ JK_EXPORT int jk_latent_attention(const void *q, const void *pages, void *out, f
         }
         return JK_OK;
     }
-    LatentAttnArgs a{q, pages, out, part, positions, row_req, block_table, T, H, R, dr, page_size, max_blocks, splits, scale};
+    LatentAttnArgs a{q, pages, out, part, positions, row_req, block_table, T, H, R, dr, page_size, max_blocks, splits, scale, window};
     const size_t smem = ((size_t)LA_WARPS * D + 32 * (size_t)(D + 1)) * sizeof(float);
     JK_REQUIRE(smem <= 220 * 1024, "latent_attention: rows of %d elements do not fit shared memory", D);
     dim3 grid((H + LA_WARPS - 1) / LA_WARPS, T, splits);
@@ -1308,10 +1326,13 @@ JK_EXPORT int jk_selective_scan(const float *x, const float *low, int ld_low, in
 // The experts' products then run over the entries, expert after expert, as tiles of the grouped kernels below; an
 // expert's input is score * h, which the first product applies to its sums (W (s h) = s (W h), in float32) before the
 // gate's activation.  expert_combine adds a row's `top` results in the order of its choices.
+// Options: a bias on the logits (`bias` [E]); a gate per row, sigmoid(gate_w . h), on what the sum is added to (a shared
+// unit's output that waits in delta).
 // ---------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void route_topk_kernel(const T *__restrict__ h, const float *__restrict__ router, int D, int E, int top, int *__restrict__ ids,
-                                  float *__restrict__ scores, int *__restrict__ counts, int score_form) {
+                                  float *__restrict__ scores, int *__restrict__ counts, int score_form, const float *__restrict__ bias,
+                                  const float *__restrict__ gate_w, float *__restrict__ row_gate) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float z[];        // [E]
@@ -1335,7 +1356,13 @@ __global__ void route_topk_kernel(const T *__restrict__ h, const float *__restri
             for (int c = lane; c < D; c += 32) dot = fmaf(w[c], to_f32(row[c]), dot);
         }
         dot = warp_sum(dot);
-        if (lane == 0) z[e] = dot;
+        if (lane == 0) z[e] = dot + (bias ? bias[e] : 0.f);
+    }
+    if (gate_w != nullptr && warp == nwarp - 1) {       // the row's gate on what the experts' sum is added to: sigmoid(gate_w . h)
+        float dot = 0.f;
+        for (int c = lane; c < D; c += 32) dot = fmaf(gate_w[c], to_f32(row[c]), dot);
+        dot = warp_sum(dot);
+        if (lane == 0) row_gate[t] = sigmoid_f(dot);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -1567,13 +1594,13 @@ __global__ void __launch_bounds__(256) expert_rows_kernel(const T *__restrict__ 
 // delta[t] (+)= sum over the row's choices, in their order, of y[pair_entry[t * top + k]] (times the choice's score where
 // `entry_score` is given: the form in which the score multiplies a unit's output)
 __global__ void expert_combine_kernel(const float *__restrict__ y, const int *__restrict__ pair_entry, float *__restrict__ delta, int D, int top,
-                                      int add, size_t total, const float *__restrict__ entry_score) {
+                                      int add, size_t total, const float *__restrict__ entry_score, const float *__restrict__ row_gate) {
     pdl_trigger();
     pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / D;
         const int c = (int)(i % D);
-        float v = add ? delta[i] : 0.f;
+        float v = add ? (row_gate ? delta[i] * row_gate[t] : delta[i]) : 0.f;
         for (int k = 0; k < top; ++k) {
             const int entry = pair_entry[t * top + k];
             v = entry_score ? fmaf(entry_score[entry], y[(size_t)entry * D + c], v) : v + y[(size_t)entry * D + c];
@@ -1583,23 +1610,24 @@ __global__ void expert_combine_kernel(const float *__restrict__ y, const int *__
 }
 
 // ints of workspace (`route`) that T rows need: counts [E], starts [E + 1], ids, entry_row, pair_entry [T top] and, as
-// floats, scores and entry_score [T top]
-JK_EXPORT long long jk_routed_experts_workspace(int T, int E, int top) { return 2LL * E + 1 + 5LL * T * top + 16; }
+// floats, scores and entry_score [T top] and the rows' gates [T]
+JK_EXPORT long long jk_routed_experts_workspace(int T, int E, int top) { return 2LL * E + 1 + 5LL * T * top + T + 16; }
 
 // h [T, D] (type T) -> delta [T, D] float32 (add: on top of what is there).  entries [T top, D]-sized buffers: `act`
 // [T top, ff] of the activation type, `y` [T top, D] float32.
 JK_EXPORT int jk_routed_experts(const void *h, const float *router, const void *w_gate_up, const void *w_down, float *delta, int add,
                                 int dtype, int T, int D, int ff, int E, int top, int actf, int *route, void *act, float *y,
-                                int score_form, float limit, cudaStream_t stream) {
+                                int score_form, float limit, const float *router_bias, const float *gate_w, cudaStream_t stream) {
     if (T == 0) return JK_OK;
+    JK_REQUIRE(gate_w == nullptr || add, "routed_experts: a gate on a shared unit's output that is not there");
     JK_REQUIRE(h && router && w_gate_up && w_down && delta && route && act && y, "routed_experts: an argument is missing");
     JK_REQUIRE(D > 0 && ff > 0 && E > 0 && top > 0 && top <= E, "routed_experts: %d experts, %d a row, sizes %d and %d", E, top, D, ff);
     JK_REQUIRE((size_t)E * sizeof(float) <= 40 * 1024, "routed_experts: %d experts exceed the router's shared memory", E);
     const int pairs = T * top;
     int *counts = route, *starts = counts + E, *ids = starts + E + 1, *entry_row = ids + pairs, *pair_entry = entry_row + pairs;
-    float *scores = (float *)(pair_entry + pairs), *entry_score = scores + pairs;
+    float *scores = (float *)(pair_entry + pairs), *entry_score = scores + pairs, *row_gate = gate_w ? entry_score + pairs : nullptr;
     if (cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)E, stream) != cudaSuccess) JK_FAIL(JK_CUDA_ERROR, "routed_experts: clearing the counts failed");
-#define LAUNCH(TT) jk_launch(route_topk_kernel<TT>, dim3(T), dim3(128), (size_t)E * sizeof(float), stream, (const TT *)h, router, D, E, top, ids, scores, counts, score_form)
+#define LAUNCH(TT) jk_launch(route_topk_kernel<TT>, dim3(T), dim3(128), (size_t)E * sizeof(float), stream, (const TT *)h, router, D, E, top, ids, scores, counts, score_form, router_bias, gate_w, row_gate)
     BLOCKS_BY_DTYPE(dtype, "route_topk", LAUNCH);
 #undef LAUNCH
     JK_CHECK_LAUNCH("route_topk");
@@ -1637,12 +1665,40 @@ JK_EXPORT int jk_routed_experts(const void *h, const float *router, const void *
     }
     const size_t total = (size_t)T * D;
     jk_launch(expert_combine_kernel, dim3((int)std::min<size_t>((total + 255) / 256, 148 * 16)), dim3(256), 0, stream, (const float *)y,
-              (const int *)pair_entry, delta, D, top, add, total, out_score);
+              (const int *)pair_entry, delta, D, top, add, total, out_score, (const float *)row_gate);
     JK_CHECK_LAUNCH("expert_combine");
     return JK_OK;
 }
 // kernels that one call of jk_routed_experts launches (the clearing of the counts included)
 JK_EXPORT int jk_routed_experts_launches() { return 6; }
+
+// ---------------------------------------------------------------------------------------------------------------
+// x[t] += table[index[t]] (index null: row `fixed` for every t): learned position vectors picked by the rows' positions,
+// or one vector of a table added to the whole stream.  The table is float32 or of the compute type; the sum is float32.
+// ---------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rows_kernel(float *__restrict__ x, const T *__restrict__ table, const int *__restrict__ index, int fixed, int d, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / d;
+        const int row = index ? index[t] : fixed;
+        x[i] += to_f32(table[(size_t)row * d + (i % d)]);
+    }
+}
+
+JK_EXPORT int jk_add_rows(float *x, const void *table, int table_dtype, int table_rows, const int *index, int fixed, int rows, int d,
+                          cudaStream_t stream) {
+    if (rows == 0) return JK_OK;
+    JK_REQUIRE(x && table && d > 0 && table_rows > 0 && (index || (fixed >= 0 && fixed < table_rows)), "add_rows: row %d of a table of %d", fixed, table_rows);
+    const size_t total = (size_t)rows * d;
+    const int blocks = (int)std::min<size_t>((total + 255) / 256, 148 * 16);
+#define LAUNCH(TT) jk_launch(add_rows_kernel<TT>, dim3(blocks), dim3(256), 0, stream, x, (const TT *)table, index, fixed, d, total)
+    BLOCKS_BY_DTYPE(table_dtype, "add_rows", LAUNCH);
+#undef LAUNCH
+    JK_CHECK_LAUNCH("add_rows");
+    return JK_OK;
+}
 
 // ---------------------------------------------------------------------------------------------------------------
 // logits <- cap * tanh(logits / cap)

@@ -140,6 +140,16 @@ static inline int jk_epilogue_gate(int epilogue) {
     return act == GATE_GELU_TANH ? GATE_GELU_TANH : (act == GATE_RELU ? GATE_RELU : GATE_SILU);
 }
 
+// ---- the mask of a causal attention as one number --------------------------------------------
+// The first key that a query at position `pos` sees: `window` 0: every earlier key; W > 0: a sliding window of W keys
+// (pos - W + 1, not below 0); -C < 0: the keys of the query's own chunk of C positions, counted from position 0 of the
+// sequence (pos / C * C).  It never falls as `pos` grows.
+__host__ __device__ __forceinline__ int jk_mask_lo(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos / (-window) * (-window);
+    return 0;
+}
+
 // ---- reductions ------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -170,28 +170,33 @@ JK_EXPORT int jk_cast_rows(const float *in, void *out, int dtype, long long n, c
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Gated linear unit: out[t, c] = act(gu[t, c]) * gu[t, di + c], gu float32 [T, 2 di].
+// Gated linear unit: out[t, c] = act(gu[t, c]) * gu[t, di + c], gu float32 [T, 2 di]; act 6: the clamped unit with `limit`.
 // ---------------------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void glu_kernel(const float *__restrict__ gu, T *__restrict__ out, int di, size_t total, int act) {
+__global__ void glu_kernel(const float *__restrict__ gu, T *__restrict__ out, int di, size_t total, int act, float limit) {
     pdl_trigger();
     pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / di, c = i % di;
         const float g = gu[t * 2 * di + c], u = gu[t * 2 * di + di + c];
+        if (act == 6) {         // the clamped unit: g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit)
+            const float gc = fminf(g, limit), uc = fminf(fmaxf(u, -limit), limit);
+            out[i] = from_f32<T>(gc / (1.f + expf(-1.702f * gc)) * (uc + 1.f));
+            continue;
+        }
         out[i] = from_f32<T>(apply_act(act, g) * u);
     }
 }
 
-JK_EXPORT int jk_glu(const float *gu, void *out, int dtype, int ntok, int di, int act, cudaStream_t stream) {
+JK_EXPORT int jk_glu(const float *gu, void *out, int dtype, int ntok, int di, int act, float limit, cudaStream_t stream) {
     if (ntok == 0) return JK_OK;
     JK_REQUIRE(gu && out && ntok > 0 && di > 0, "glu: rows %d, width %d", ntok, di);
     const size_t total = (size_t)ntok * di;
     const int blocks = (int)std::min<size_t>((total + 255) / 256, 148 * 16);
     if (dtype == JK_F32)
-        jk_launch(glu_kernel<float>, dim3(blocks), dim3(256), 0, stream, gu, (float *)out, di, total, act);
+        jk_launch(glu_kernel<float>, dim3(blocks), dim3(256), 0, stream, gu, (float *)out, di, total, act, limit);
     else if (dtype == JK_BF16)
-        jk_launch(glu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, gu, (__nv_bfloat16 *)out, di, total, act);
+        jk_launch(glu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, gu, (__nv_bfloat16 *)out, di, total, act, limit);
     else
         JK_FAIL(JK_UNSUPPORTED, "glu: dtype %d", dtype);
     JK_CHECK_LAUNCH("glu");
@@ -222,7 +227,10 @@ struct ConvQkvArgs {
     float eps;
     int rot_half;               // 1: element i < rot_dims / 2 of a head pairs with element i + rot_dims / 2 (else 2i with 2i + 1)
     float rot_mag;              // factor of cos and sin
-    int head_norm;              // 1: after the rotation every head of q and k is divided by its root mean square (eps inside)
+    int head_norm;              // 1: after the rotation every head of q and k is divided by its root mean square (eps inside);
+                                // 2: BEFORE the rotation every head of q and k passes an RMS norm whose weight (norm_q, norm_k:
+                                // [dk], shared by the heads) multiplies it; the whole-projection norm is then off
+    const float *bias;          // [ld] or null: added to the projection's columns as they are read (no convolution then)
     const int *positions, *row_req, *req_start, *slot_ids, *block_table;
     int max_blocks, page_size;
     void *q_out, *k_pages, *v_pages;
@@ -249,7 +257,7 @@ __global__ void conv_qkv_kernel(ConvQkvArgs a) {
         else { col = a.v_off + c - a.nq - a.nk; w = a.conv_v ? a.conv_v + (size_t)(c - a.nq - a.nk) * a.taps : nullptr; }
         float acc;
         if (w == nullptr) {
-            acc = a.u[(size_t)t * a.ld + col];
+            acc = a.u[(size_t)t * a.ld + col] + (a.bias ? a.bias[col] : 0.f);
         } else {
             acc = 0.f;
             for (int j = 0; j < a.taps; ++j) {
@@ -266,12 +274,13 @@ __global__ void conv_qkv_kernel(ConvQkvArgs a) {
     }
     const float sum_q = block_sum(ssq, scratch);
     const float sum_k = a.nk > 0 ? block_sum(ssk, scratch) : 0.f;
-    const float inv_q = a.norm_q ? 1.f / sqrtf(sum_q / (float)a.nq + a.eps) : 1.f;
-    const float inv_k = (a.norm_k && a.nk > 0) ? 1.f / sqrtf(sum_k / (float)a.nk + a.eps) : 1.f;
+    const bool whole = a.head_norm != 2;        // the norm over a whole projection
+    const float inv_q = (whole && a.norm_q) ? 1.f / sqrtf(sum_q / (float)a.nq + a.eps) : 1.f;
+    const float inv_k = (whole && a.norm_k && a.nk > 0) ? 1.f / sqrtf(sum_k / (float)a.nk + a.eps) : 1.f;
     for (int c = threadIdx.x; c < a.nq + a.nk; c += blockDim.x) {
         const bool is_q = c < a.nq;
         const int cc = is_q ? c : c - a.nq;
-        const float *nw = is_q ? a.norm_q : a.norm_k;
+        const float *nw = whole ? (is_q ? a.norm_q : a.norm_k) : nullptr;
         y[c] = y[c] * (is_q ? inv_q : inv_k) * (nw ? nw[cc] : 1.f);
     }
     __syncthreads();
@@ -289,7 +298,32 @@ __global__ void conv_qkv_kernel(ConvQkvArgs a) {
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
         const int half = a.rot_dims >> 1, heads = (a.nq + a.nk) / a.dk;
         for (int hh = warp; hh < heads; hh += nwarp) {
-            const float *yh = y + (size_t)hh * a.dk;
+            float *yh = y + (size_t)hh * a.dk;
+            if (a.head_norm == 2) {
+                // the norm first: the head's mean square, its weight; then the rotation of the normed elements
+                const float *nw = hh * a.dk < a.nq ? a.norm_q : a.norm_k;
+                float s2 = 0.f;
+                for (int e = lane; e < a.dk; e += 32) s2 += yh[e] * yh[e];
+                const float inv2 = 1.f / sqrtf(warp_sum(s2) / (float)a.dk + a.eps);
+                for (int e = lane; e < a.dk; e += 32) yh[e] = yh[e] * inv2 * (nw ? nw[e] : 1.f);
+                __syncwarp();
+                for (int e = lane; e < a.dk; e += 32) {
+                    float val = yh[e];
+                    if (e < a.rot_dims) {
+                        const bool first = a.rot_half ? e < half : !(e & 1);
+                        const int pair = a.rot_half ? (first ? e : e - half) : e >> 1;
+                        const float other = yh[a.rot_half ? (first ? e + half : e - half) : (first ? e + 1 : e - 1)];
+                        float sn, cs;
+                        sincosf(fpos * a.freq[pair], &sn, &cs);
+                        sn *= a.rot_mag; cs *= a.rot_mag;
+                        val = first ? val * cs - other * sn : val * cs + other * sn;
+                    }
+                    const int c = hh * a.dk + e;
+                    if (c < a.nq) q_out[c] = from_f32<T>(val);
+                    else ((T *)a.k_pages)[(k_row + (size_t)((c - a.nq) / a.dk) * a.page_size) * a.dk + e] = from_f32<T>(val);
+                }
+                continue;
+            }
             float ss = 0.f;
             for (int e = lane; e < a.dk; e += 32) {
                 float val = yh[e];
@@ -378,9 +412,10 @@ JK_EXPORT int jk_conv_qkv(const float *u, int ld, int q_off, int k_off, int v_of
                           const float *norm_q, const float *norm_k, float eps, const float *freq, int rot_dims, float *tail,
                           const int *positions, const int *row_req, const int *req_start, const int *slot_ids,
                           const int *block_table, int max_blocks, int page_size, void *q_out, void *k_pages, void *v_pages,
-                          int dtype, int T, int nreq, int rot_half, float rot_mag, int head_norm, cudaStream_t stream) {
+                          int dtype, int T, int nreq, int rot_half, float rot_mag, int head_norm, const float *bias, cudaStream_t stream) {
     if (T == 0) return JK_OK;
     ConvQkvArgs a;
+    a.bias = bias;
     a.u = u; a.ld = ld; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off;
     a.nq = heads * dk; a.nk = has_kv ? kv_heads * dk : 0; a.nv = has_kv ? kv_heads * dv : 0;
     a.conv_q = conv_q; a.conv_k = conv_k; a.conv_v = conv_v; a.norm_q = norm_q; a.norm_k = norm_k; a.freq = freq; a.tail = tail;
@@ -391,6 +426,7 @@ JK_EXPORT int jk_conv_qkv(const float *u, int ld, int q_off, int k_off, int v_of
     const bool conv = conv_q || conv_k || conv_v;
     JK_REQUIRE(u && q_out && positions && row_req && req_start && heads > 0 && dk > 0, "conv_qkv: an argument is missing");
     JK_REQUIRE(!has_kv || (k_pages && v_pages && block_table && kv_heads > 0 && dv > 0 && page_size > 0), "conv_qkv: keys without a cache");
+    JK_REQUIRE(!(conv && bias), "conv_qkv: a bias with a convolution is not built");
     JK_REQUIRE(!conv || (taps >= 1 && (taps == 1 || (tail && slot_ids))), "conv_qkv: a convolution of %d taps without its tails", taps);
     JK_REQUIRE(rot_dims >= 0 && rot_dims <= dk && rot_dims % 2 == 0 && (rot_dims == 0 || freq), "conv_qkv: rotation of %d of %d elements", rot_dims, dk);
     const int C = a.nq + a.nk + a.nv;
@@ -1155,5 +1191,128 @@ JK_EXPORT int jk_act_rows(const float *u, int ld, void *out, int dtype, int T, i
     else
         JK_FAIL(JK_UNSUPPORTED, "act_rows: dtype %d", dtype);
     JK_CHECK_LAUNCH("act_rows");
+    return JK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The gated delta rule: per request and head, over the request's rows in order,
+//     S <- g_t S;   w_t = beta_t (v_t - S^T k_t);   S <- S + k_t w_t^T;   o_t = S^T q_t          S [dk, dv], float32
+// so a row's read-out sees its own write.  q and k come as float32 rows `c` (after their convolutions and activations),
+// one head per key/value group (query head h reads group h / (heads / groups)), and are made unit vectors here,
+// x / sqrt(sum(x^2) + unit_eps), q also times q_scale; v likewise from `c`, one head per query head.  The write strength
+// beta_t = sigmoid(u[t, b_off + h]) and the decay g_t = exp(-exp(A_log[h]) softplus(u[t, a_off + h] + dt_bias[h])) are
+// formed here in float32 from the float32 projection rows `u`.  S lives in state[slot, h] between steps.
+//
+// A block owns DR_COLS value columns of one (request, head); DR_LANES neighbouring lanes share a column and keep the
+// key channels part, part + DR_LANES, ... of it in registers (NPER each).  Rows pass shared memory DR_ROWS at a time: the
+// block norms q and k (a warp a row), stages its columns of v, the rows' beta and g.  A row then costs two sums over the
+// lanes of a column (S^T k before the write, S^T q after it) and 3 NPER multiply-adds a thread.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int DR_LANES = 8, DR_COLS = 16, DR_THREADS = DR_LANES * DR_COLS, DR_ROWS = 16;
+
+struct DeltaArgs {
+    const float *c;             // [T, ld_c]: q at q_off (groups * dk), k at k_off (groups * dk), v at v_off (heads * dv)
+    int ld_c, q_off, k_off, v_off;
+    const float *u;             // [T, ld_u]: the write strength's logit at b_off + h, the decay's at a_off + h
+    int ld_u, b_off, a_off;
+    const float *A_log, *dt_bias;       // [heads]
+    int heads, groups, dk, dv;
+    float q_scale, unit_eps;
+    float *state;               // [slots, heads, dk, dv]
+    const int *req_start, *slot_ids;
+    float *out;                 // [T, heads * dv]
+};
+
+template <int NPER>
+__global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(DeltaArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int KP = NPER * DR_LANES;         // key channels, padded: the padding holds zeros
+    __shared__ float ks[DR_ROWS][KP], qs[DR_ROWS][KP], vs[DR_ROWS][DR_COLS], gs[DR_ROWS], bs[DR_ROWS];
+    const int h = blockIdx.x, req = blockIdx.y, col0 = blockIdx.z * DR_COLS;
+    const int group = h / (a.heads / a.groups);
+    const int part = threadIdx.x % DR_LANES, cl = threadIdx.x / DR_LANES, col = col0 + cl;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool live = col < a.dv;
+    const int first = a.req_start[req], n = a.req_start[req + 1] - first;
+    float *S = a.state + (((size_t)a.slot_ids[req] * a.heads + h) * a.dk) * a.dv;
+    float s[NPER];
+#pragma unroll
+    for (int r = 0; r < NPER; ++r) {
+        const int i = part + DR_LANES * r;
+        s[r] = (live && i < a.dk) ? S[(size_t)i * a.dv + col] : 0.f;
+    }
+    const float rate = expf(a.A_log[h]), bias = a.dt_bias[h];
+    for (int r0 = 0; r0 < n; r0 += DR_ROWS) {
+        const int nr = min(DR_ROWS, n - r0);
+        __syncthreads();        // the rows before are done with
+        for (int r = warp; r < nr; r += DR_THREADS / 32) {
+            const float *row = a.c + (size_t)(first + r0 + r) * a.ld_c;
+            const float *kr = row + a.k_off + (size_t)group * a.dk, *qr = row + a.q_off + (size_t)group * a.dk;
+            float sk = 0.f, sq = 0.f;
+            for (int i = lane; i < a.dk; i += 32) { sk = fmaf(kr[i], kr[i], sk); sq = fmaf(qr[i], qr[i], sq); }
+            const float ik = 1.f / sqrtf(warp_sum(sk) + a.unit_eps), iq = a.q_scale / sqrtf(warp_sum(sq) + a.unit_eps);
+            for (int i = lane; i < KP; i += 32) {
+                ks[r][i] = i < a.dk ? kr[i] * ik : 0.f;
+                qs[r][i] = i < a.dk ? qr[i] * iq : 0.f;
+            }
+        }
+        for (int i = threadIdx.x; i < nr * DR_COLS; i += DR_THREADS) {
+            const int r = i / DR_COLS, cc = i % DR_COLS;
+            vs[r][cc] = col0 + cc < a.dv ? a.c[(size_t)(first + r0 + r) * a.ld_c + a.v_off + (size_t)h * a.dv + col0 + cc] : 0.f;
+        }
+        if (threadIdx.x < nr) {
+            const float *urow = a.u + (size_t)(first + r0 + threadIdx.x) * a.ld_u;
+            const float z = urow[a.a_off + h] + bias;
+            const float sp = z > 20.f ? z : log1pf(expf(z));
+            gs[threadIdx.x] = expf(-rate * sp);
+            bs[threadIdx.x] = sigmoid_f(urow[a.b_off + h]);
+        }
+        __syncthreads();
+        for (int r = 0; r < nr; ++r) {
+            const float g = gs[r], beta = bs[r];
+            float kv = 0.f;
+#pragma unroll
+            for (int j = 0; j < NPER; ++j) kv = fmaf(s[j], ks[r][part + DR_LANES * j], kv);
+            kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+            kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+            kv += __shfl_xor_sync(0xffffffffu, kv, 4);
+            const float w = beta * (vs[r][cl] - g * kv);
+            float o = 0.f;
+#pragma unroll
+            for (int j = 0; j < NPER; ++j) {
+                s[j] = fmaf(ks[r][part + DR_LANES * j], w, g * s[j]);
+                o = fmaf(s[j], qs[r][part + DR_LANES * j], o);
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            o += __shfl_xor_sync(0xffffffffu, o, 4);
+            if (part == 0 && live) a.out[(size_t)(first + r0 + r) * a.heads * a.dv + (size_t)h * a.dv + col] = o;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < NPER; ++r) {
+        const int i = part + DR_LANES * r;
+        if (live && i < a.dk) S[(size_t)i * a.dv + col] = s[r];
+    }
+}
+
+JK_EXPORT int jk_delta_rule(const float *c, int ld_c, int q_off, int k_off, int v_off, const float *u, int ld_u, int b_off, int a_off,
+                            const float *A_log, const float *dt_bias, int heads, int groups, int dk, int dv, float q_scale, float unit_eps,
+                            float *state, const int *req_start, const int *slot_ids, int nreq, float *out, cudaStream_t stream) {
+    if (nreq == 0) return JK_OK;
+    JK_REQUIRE(c && u && A_log && dt_bias && state && req_start && slot_ids && out, "delta_rule: an argument is missing");
+    JK_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0 && dk > 0 && dv > 0, "delta_rule: %d heads on %d groups, sizes %d and %d", heads, groups, dk, dv);
+    JK_REQUIRE(dk <= 32 * DR_LANES, "delta_rule: key heads of %d exceed %d", dk, 32 * DR_LANES);
+    JK_REQUIRE(nreq <= 65535 && (dv + DR_COLS - 1) / DR_COLS <= 65535, "delta_rule: %d requests exceed one launch", nreq);
+    DeltaArgs a{c, ld_c, q_off, k_off, v_off, u, ld_u, b_off, a_off, A_log, dt_bias, heads, groups, dk, dv, q_scale, unit_eps, state, req_start,
+                slot_ids, out};
+    const dim3 grid(heads, nreq, (dv + DR_COLS - 1) / DR_COLS);
+    const int per = (dk + DR_LANES - 1) / DR_LANES;
+    if (per <= 4) jk_launch(delta_rule_kernel<4>, grid, dim3(DR_THREADS), 0, stream, a);
+    else if (per <= 8) jk_launch(delta_rule_kernel<8>, grid, dim3(DR_THREADS), 0, stream, a);
+    else if (per <= 16) jk_launch(delta_rule_kernel<16>, grid, dim3(DR_THREADS), 0, stream, a);
+    else jk_launch(delta_rule_kernel<32>, grid, dim3(DR_THREADS), 0, stream, a);
+    JK_CHECK_LAUNCH("delta_rule");
     return JK_OK;
 }

@@ -22,6 +22,7 @@
 #include "runner.h"
 
 #include <cublas_v2.h>
+#include <cstdlib>
 #include <mutex>
 
 JK_DEFINE_ERROR_BUFFER(jk_runner)
@@ -181,7 +182,7 @@ bool qkv_fusable(const Run &r, const RunnerOp &op) {
 bool consumer_takes_norm(const Run &r, const RunnerOp &norm, const RunnerOp &next, int T) {
     if (next.in_slot != norm.out_slot) return false;
     if (next.kind == OP_GATE_UP)
-        return r.route(T, next.n, next.k, jk::PRODUCT_SWIGLU) == jk::ROUTE_SMALL && g_fns.linear_small_norm_supports(T, next.n, next.k);
+        return next.act != RUNNER_ACT_SWISH_CLAMP && r.route(T, next.n, next.k, jk::PRODUCT_SWIGLU) == jk::ROUTE_SMALL && g_fns.linear_small_norm_supports(T, next.n, next.k);
     if (next.kind == OP_QKV) return qkv_fusable(r, next) && g_fns.linear_small_qkv_supports(T, next.k, next.head_dim);
     return false;
 }
@@ -285,7 +286,7 @@ int run_attention(Run &r, const RunnerOp &op) {
     }
     if (n_short > 0) {
         const int context = r.st.context > 0 ? r.st.context : op.max_positions;
-        const int splits = jk::decode_splits(n_short, nkvh, nh / nkvh, jk::decode_keys_hint(context, op.window), r.env.routing.sms, dh);
+        const int splits = jk::decode_splits(n_short, nkvh, nh / nkvh, jk::decode_keys_hint(context, std::abs(op.window)), r.env.routing.sms, dh);
         void *scratch = nullptr;
         const long long need = 4 * jk::decode_scratch_floats(n_short, nh, dh, splits);
         if (need > 0)
@@ -346,16 +347,17 @@ int run_gate_up(Run &r, const RunnerOp &op, const FusedNorm &fused) {
     if (int rc = r.slot(op.in_slot, (long long)r.elem() * T * d, &h, "gate/up's activations")) return rc;
     if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * di, &act, "the feed-forward's inner activations")) return rc;
     // the gate's activation rides above the epilogue's code (common.cuh: gated_unit)
-    JK_REQUIRE(op.act == RUNNER_ACT_NONE || op.act == RUNNER_ACT_SILU || op.act == RUNNER_ACT_GELU_TANH || op.act == RUNNER_ACT_RELU,
-               "runner: a gated unit with activation %d is not built", op.act);
-    const bool other_gate = op.act == RUNNER_ACT_GELU_TANH || op.act == RUNNER_ACT_RELU;      // not silu: the unfused unit is the mixers module's
+    JK_REQUIRE(op.act == RUNNER_ACT_NONE || op.act == RUNNER_ACT_SILU || op.act == RUNNER_ACT_GELU_TANH || op.act == RUNNER_ACT_RELU ||
+               op.act == RUNNER_ACT_SWISH_CLAMP, "runner: a gated unit with activation %d is not built", op.act);
+    const bool clamped = op.act == RUNNER_ACT_SWISH_CLAMP;      // no product has this unit in its epilogue: product, then the unit's kernel
+    const bool other_gate = op.act == RUNNER_ACT_GELU_TANH || op.act == RUNNER_ACT_RELU || clamped;      // not silu: the unfused unit is the mixers module's
     const int gate_bits = other_gate ? (op.act << 8) : 0;
-    if (fused.norm != nullptr) {
+    if (fused.norm != nullptr && !clamped) {
         RUN(linear_small, g_fns.linear_small_norm(h, op.w, act, T, di, d, di, 1 | gate_bits, fused.sumsq, fused.norm->eps, nullptr, nullptr, nullptr,
                                                   1.f, r.env.status, ro.sms, r.stream));
         return JK_OK;
     }
-    if (r.env.dtype == JK_BF16) {
+    if (r.env.dtype == JK_BF16 && !clamped) {
         switch (r.route(T, di, d, jk::PRODUCT_SWIGLU)) {
             case jk::ROUTE_SMALL:
                 RUN(linear_small, g_fns.linear_small(h, op.w, act, T, di, d, di, 1 | gate_bits, ro.sms, r.stream));
@@ -374,12 +376,14 @@ int run_gate_up(Run &r, const RunnerOp &op, const FusedNorm &fused) {
     if (int rc = r.slot(SLOT_TMP, 4LL * T * 2 * di, &tmp, "the gate/up product")) return rc;
     if (r.env.dtype == JK_F32) {
         RUN(elementwise, g_fns.gemm_f32((const float *)h, d, (const float *)op.w, d, nullptr, (float *)tmp, 2 * di, T, 2 * di, d, r.stream));
+    } else if (clamped) {
+        if (int rc = product_f32(r, h, op.w, nullptr, (float *)tmp, T, 2 * di, d)) return rc;       // by the rows' route, float32 sums
     } else {
         if (int rc = lt_product(h, op.w, (float *)tmp, T, 2 * di, d, r.buf, r.stream)) return rc;
     }
     if (other_gate) {
         JK_REQUIRE(g_fns.glu != nullptr, "runner: the unfused gated unit with activation %d needs the mixers module", op.act);
-        RUN(mixers, g_fns.glu((const float *)tmp, act, r.env.dtype, T, di, op.act, r.stream));
+        RUN(mixers, g_fns.glu((const float *)tmp, act, r.env.dtype, T, di, op.act, op.limit, r.stream));
         return JK_OK;
     }
     RUN(elementwise, g_fns.swiglu(tmp, JK_F32, act, r.env.dtype, T, di, r.stream));
@@ -486,7 +490,7 @@ int run_conv_qkv(Run &r, const RunnerOp &op) {
     RUN(mixers, g_fns.conv_qkv((const float *)u, op.ld, op.q_off, op.k_off, op.v_off, op.heads, op.kv_heads, op.head_dim, dv, op.has_kv,
                                op.conv_q, op.conv_k, op.conv_v, op.taps, op.norm_q, op.norm_k, op.eps, op.freq, op.rot_dims, op.state,
                                r.st.positions, r.st.row_req, r.st.req_start, r.st.slot_ids, table, r.env.max_blocks, r.env.page_size, q,
-                               op.k_pages, op.v_pages, r.env.dtype, T, r.st.nreq, op.rot_half, op.rot_mag, op.head_norm, r.stream));
+                               op.k_pages, op.v_pages, r.env.dtype, T, r.st.nreq, op.rot_half, op.rot_mag, op.head_norm, op.bias, r.stream));
     if (op.taps > 1) ++g_launches;      // the tails' kernel
     return JK_OK;
 }
@@ -558,13 +562,18 @@ int run_latent_qkv(Run &r, const RunnerOp &op) {
     const int T = r.st.ntok, H = op.heads, D = op.rank + op.rot_width;
     void *u, *q_full, *q_plain;
     if (int rc = r.slot(op.in_slot, 4LL * T * op.ld, &u, "the query and latent projection")) return rc;
-    if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * H * D, &q_full, "the queries")) return rc;
-    if (int rc = r.slot(op.out2_slot, (long long)r.elem() * T * H * op.head_dim, &q_plain, "the queries' plain parts")) return rc;
+    if (op.q_rank > 0) {        // the queries' own latent vector, normed; the heads' queries are made by the records that follow
+        q_full = nullptr;
+        if (int rc = r.slot(op.out2_slot, (long long)r.elem() * T * op.q_rank, &q_plain, "the queries' latent vector")) return rc;
+    } else {
+        if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * H * D, &q_full, "the queries")) return rc;
+        if (int rc = r.slot(op.out2_slot, (long long)r.elem() * T * H * op.head_dim, &q_plain, "the queries' plain parts")) return rc;
+    }
     const int *table = r.st.block_tables[op.cache_group];
     JK_REQUIRE(table != nullptr, "runner: a latent attention writes the cache of group %d, whose block table the step lacks", op.cache_group);
     RUN(blocks, g_fns.latent_qkv((const float *)u, op.ld, op.q_off, op.k_off, H, op.head_dim, op.rot_width, op.rank, op.rot_dims, op.freq,
                                  op.rot_mag, op.norm_k, op.eps, r.st.positions, r.st.row_req, table, r.env.max_blocks, r.env.page_size,
-                                 q_plain, q_full, op.k_pages, r.env.dtype, T, r.stream));
+                                 q_plain, q_full, op.k_pages, r.env.dtype, T, op.q_rank > 0 ? op.norm_q : nullptr, op.q_rank, r.stream));
     return JK_OK;
 }
 
@@ -600,12 +609,14 @@ int run_latent_attention(Run &r, const RunnerOp &op) {
     if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * H * op.rank, &o, "a latent attention's output")) return rc;
     const int *table = r.st.block_tables[op.cache_group];
     JK_REQUIRE(table != nullptr, "runner: a latent attention reads the cache of group %d, whose block table the step lacks", op.cache_group);
-    const int splits = latent_splits(T, H, r.st.context > 0 ? r.st.context : op.max_positions, r.env.routing.sms);
+    int reach = r.st.context > 0 ? r.st.context : op.max_positions;
+    if (op.window > 0) reach = std::min(reach, op.window);
+    const int splits = latent_splits(T, H, reach, r.env.routing.sms);
     void *part = nullptr;
     if (splits > 1)
         if (int rc = r.slot(SLOT_DECODE, 4 * g_fns.latent_attention_scratch(T, H, op.rank, splits), &part, "the ranges of a latent attention")) return rc;
     RUN(blocks, g_fns.latent_attention(q, op.k_pages, o, (float *)part, r.env.dtype, r.st.positions, r.st.row_req, table, r.env.max_blocks,
-                                       r.env.page_size, T, H, op.rank, op.rot_width, op.softmax_scale, splits, r.st.req_start, r.st.nreq, r.stream));
+                                       r.env.page_size, T, H, op.rank, op.rot_width, op.softmax_scale, splits, r.st.req_start, r.st.nreq, op.window, r.stream));
     if (splits > 1) ++g_launches;
     return JK_OK;
 }
@@ -653,7 +664,7 @@ int run_experts(Run &r, const RunnerOp &op) {
     if (int rc = r.slot(SLOT_TMP, 4LL * T * op.top * op.n, &y, "the experts' results")) return rc;
     JK_REQUIRE(!r.pending, "runner: routed experts while another product waits to be added");
     RUN(blocks, g_fns.routed_experts(h, op.vec, op.w, op.w3, (float *)delta, op.add, r.env.dtype, T, op.n, op.ff, op.experts, op.top, op.act,
-                                     (int *)route, act, (float *)y, op.score_form, op.limit, r.stream));
+                                     (int *)route, act, (float *)y, op.score_form, op.limit, op.router_bias, op.gate_w, r.stream));
     g_launches += g_fns.routed_experts_launches() - 1;
     if (op.into_stream) {       // a block without a norm on the sublayer's output: the next norm adds it
         r.pending = true;
@@ -682,6 +693,36 @@ int run_activate(Run &r, const RunnerOp &op) {
     if (int rc = r.slot(op.in_slot, 4LL * T * ld, &u, "an activation's input")) return rc;
     if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.n, &out, "an activation's output")) return rc;
     RUN(mixers, g_fns.act_rows((const float *)u, ld, out, r.env.dtype, T, op.n, op.act, r.stream));
+    return JK_OK;
+}
+
+int run_add_rows(Run &r, const RunnerOp &op) {
+    JK_REQUIRE(g_fns.add_rows != nullptr, "runner: rows of a table added to the stream need the blocks module, which was not bound");
+    const int T = r.st.ntok;
+    void *x;
+    if (int rc = r.slot(SLOT_X, 4LL * T * op.n, &x, "the stream")) return rc;
+    if (int rc = flush_pending(r, T, op.n)) return rc;
+    RUN(blocks, g_fns.add_rows((float *)x, op.w, op.w_dtype, op.k, op.fixed_row < 0 ? r.st.positions : nullptr, op.fixed_row, T, op.n, r.stream));
+    return JK_OK;
+}
+
+// DELTA_RULE: ld = width of the convolved rows in in_slot (q at q_off, k at k_off, v at v_off); r_off = width of SLOT_TMP's rows
+// (the write strength's logit at b_off + h, the decay's at a_off + h, the gate at g_off)
+int run_delta_rule(Run &r, const RunnerOp &op) {
+    if (int rc = need_mixers("a delta rule")) return rc;
+    JK_REQUIRE(g_fns.delta_rule != nullptr, "runner: a delta rule needs its kernel, which was not bound");
+    const int T = r.st.ntok, dv = op.v_head_dim;
+    void *c, *u, *mix, *out;
+    if (int rc = r.slot(op.in_slot, 4LL * T * op.ld, &c, "the convolved q/k/v")) return rc;
+    if (int rc = r.slot(SLOT_TMP, 4LL * T * op.r_off, &u, "the projection that holds a delta rule's logits and gate")) return rc;
+    if (int rc = r.slot(SLOT_SCAN, 4LL * T * op.heads * dv, &mix, "a recurrence's output")) return rc;
+    if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.heads * dv, &out, "a delta rule's output")) return rc;
+    JK_REQUIRE(r.st.slot_ids != nullptr && op.state != nullptr, "runner: a recurrence without its state slots");
+    RUN(mixers, g_fns.delta_rule((const float *)c, op.ld, op.q_off, op.k_off, op.v_off, (const float *)u, op.r_off, op.b_off, op.a_off, op.a_log,
+                                 op.dt_bias, op.heads, op.groups, op.head_dim, dv, op.q_scale, op.unit_eps, op.state, r.st.req_start,
+                                 r.st.slot_ids, r.st.nreq, (float *)mix, r.stream));
+    RUN(mixers, g_fns.norm_gate((const float *)mix, (const float *)u, op.r_off, op.g_off, op.vec, op.eps, op.heads, dv, op.per_head_norm,
+                                op.gate_act, out, r.env.dtype, T, r.stream));
     return JK_OK;
 }
 
@@ -794,6 +835,11 @@ JK_EXPORT int jk_runner_run(const RunnerEnv *envp, const RunnerOp *ops, int firs
             case OP_SOFTCAP: rc = run_softcap(r, op); break;
             case OP_TOKEN_SHIFT: rc = run_token_shift(r, op); break;
             case OP_ACTIVATE: rc = run_activate(r, op); break;
+            case OP_ADD_ROWS:
+                hidden = op.n;
+                rc = run_add_rows(r, op);
+                break;
+            case OP_DELTA_RULE: rc = run_delta_rule(r, op); break;
             default:
                 JK_FAIL(JK_BAD_ARGUMENT, "runner_run: record %d has kind %d", i, op.kind);
         }
@@ -831,7 +877,7 @@ JK_EXPORT int jk_runner_slot_bytes(const RunnerEnv *env, const RunnerOp *ops, in
                 for (int context = 256;; context *= 2) {
                     const int c = context < op.max_positions ? context : op.max_positions;
                     for (int n = 1; n <= max_rows; ++n) {
-                        const int s = jk::decode_splits(n, op.kv_heads, op.heads / op.kv_heads, jk::decode_keys_hint(c, op.window),
+                        const int s = jk::decode_splits(n, op.kv_heads, op.heads / op.kv_heads, jk::decode_keys_hint(c, std::abs(op.window)),
                                                         env->routing.sms, op.head_dim);
                         worst = std::max(worst, jk::decode_scratch_floats(n, op.heads, op.head_dim, s));
                         if (s <= 1) break;
@@ -865,7 +911,9 @@ JK_EXPORT int jk_runner_slot_bytes(const RunnerEnv *env, const RunnerOp *ops, in
                 break;
             case OP_REINJECT: need(SLOT_X, 4 * rows * op.n); need(op.in_slot, 4 * rows * op.n); need(SLOT_ACT, e * rows * op.k); break;
             case OP_LATENT_QKV:
-                need(op.in_slot, 4 * rows * op.ld); need(op.out_slot, e * rows * op.heads * (op.rank + op.rot_width));
+                need(op.in_slot, 4 * rows * op.ld);
+                if (op.q_rank > 0) { need(op.out2_slot, e * rows * op.q_rank); break; }
+                need(op.out_slot, e * rows * op.heads * (op.rank + op.rot_width));
                 need(op.out2_slot, e * rows * op.heads * op.head_dim);
                 break;
             case OP_HEAD_LINEAR:
@@ -890,10 +938,17 @@ JK_EXPORT int jk_runner_slot_bytes(const RunnerEnv *env, const RunnerOp *ops, in
                 break;
             case OP_EXPERTS:
                 need(op.in_slot, e * rows * op.n); need(SLOT_DELTA, 4 * rows * op.n);
-                need(SLOT_ROUTE, 4 * (2LL * op.experts + 1 + 5 * rows * op.top + 16));
+                need(SLOT_ROUTE, 4 * (2LL * op.experts + 1 + 5 * rows * op.top + rows + 16));
                 need(SLOT_ACT, e * rows * op.top * op.ff); need(SLOT_TMP, 4 * rows * op.top * op.n);
                 break;
             case OP_SOFTCAP: need(op.in_slot, 4 * rows * op.n); break;
+            case OP_ADD_ROWS: need(SLOT_X, 4 * rows * op.n); break;
+            case OP_DELTA_RULE: {
+                const long long width = (long long)op.heads * op.v_head_dim;
+                need(op.in_slot, 4 * rows * op.ld); need(SLOT_TMP, 4 * rows * op.r_off); need(SLOT_SCAN, 4 * rows * width);
+                need(op.out_slot, e * rows * width);
+                break;
+            }
             default: JK_FAIL(JK_BAD_ARGUMENT, "runner_slot_bytes: record %d has kind %d", i, op.kind);
         }
     }

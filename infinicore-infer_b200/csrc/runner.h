@@ -52,10 +52,10 @@ typedef const char *(*LastErrorFn)();
 // csrc/mixers.cu
 typedef int (*LayernormFn)(const float *, const int *, int, int, const float *, const float *, float, float *, void *, int, cudaStream_t);
 typedef int (*CastRowsFn)(const float *, void *, int, long long, cudaStream_t);
-typedef int (*GluFn)(const float *, void *, int, int, int, int, cudaStream_t);
+typedef int (*GluFn)(const float *, void *, int, int, int, int, float, cudaStream_t);
 typedef int (*ConvQkvFn)(const float *, int, int, int, int, int, int, int, int, int, const float *, const float *, const float *, int,
                          const float *, const float *, float, const float *, int, float *, const int *, const int *, const int *,
-                         const int *, const int *, int, int, void *, void *, void *, int, int, int, int, float, int, cudaStream_t);
+                         const int *, const int *, int, int, void *, void *, void *, int, int, int, int, float, int, const float *, cudaStream_t);
 typedef int (*LinearScanFn)(const float *, int, int, int, int, int, int, int, int, float, const float *, const void *, int, const float *,
                             int, int, float, float *, const int *, const int *, int, int, float *, const int *, int, const int *, int,
                             const int *, int, float *, long long, int, const float *, int, int, cudaStream_t);
@@ -68,10 +68,10 @@ typedef int (*NormAddFn)(const float *, float *, const float *, float, const flo
 typedef int (*ConcatCastFn)(const float *, const float *, void *, int, int, int, cudaStream_t);
 typedef int (*AddBiasRowsFn)(float *, const float *, int, int, cudaStream_t);
 typedef int (*LatentQkvFn)(const float *, int, int, int, int, int, int, int, int, const float *, float, const float *, float, const int *,
-                           const int *, const int *, int, int, void *, void *, void *, int, int, cudaStream_t);
+                           const int *, const int *, int, int, void *, void *, void *, int, int, const float *, int, cudaStream_t);
 typedef int (*HeadLinearFn)(const void *, const void *, void *, int, int, int, int, int, int, const float *, int, cudaStream_t);
 typedef int (*LatentAttentionFn)(const void *, const void *, void *, float *, int, const int *, const int *, const int *, int, int, int,
-                                 int, int, int, float, int, const int *, int, cudaStream_t);
+                                 int, int, int, float, int, const int *, int, int, cudaStream_t);
 typedef long long (*LatentScratchFn)(int, int, int, int);
 typedef int (*CausalConvFn)(const float *, int, int, int, const float *, const float *, int, int, float *, const int *, const int *,
                             const int *, float *, void *, int, int, int, cudaStream_t);
@@ -79,10 +79,14 @@ typedef int (*SelectiveScanFn)(const float *, const float *, int, int, int, int,
                                const float *, const float *, float *, const int *, const int *, int, void *, int, float *, int, int,
                                cudaStream_t);
 typedef int (*RoutedExpertsFn)(const void *, const float *, const void *, const void *, float *, int, int, int, int, int, int, int, int,
-                               int *, void *, float *, int, float, cudaStream_t);
+                               int *, void *, float *, int, float, const float *, const float *, cudaStream_t);
 typedef long long (*RoutedWorkspaceFn)(int, int, int);
 typedef int (*CountFn)();
 typedef int (*SoftcapFn)(float *, float, long long, cudaStream_t);
+typedef int (*AddRowsFn)(float *, const void *, int, int, const int *, int, int, int, cudaStream_t);
+// csrc/mixers.cu
+typedef int (*DeltaRuleFn)(const float *, int, int, int, int, const float *, int, int, int, const float *, const float *, int, int, int, int,
+                           float, float, float *, const int *, const int *, int, float *, cudaStream_t);
 typedef int (*ArgmaxFn)(const float *, long long, int, int, int *, void *, cudaStream_t);
 typedef int (*SampleFn)(const float *, long long, int, int, const float *, const int *, const float *, const float *, int *,
                         cudaStream_t);
@@ -147,6 +151,10 @@ struct RunnerFns {
     // several few-row products of one launch (csrc/linear_small.cu); may be empty: the products then run one by one
     LinearSmallPartsFn linear_small_parts;
     SupportsFn linear_small_parts_supports;
+    // rows of a table added to the stream (csrc/blocks.cu, bound with that module) and the gated delta rule (csrc/mixers.cu,
+    // bound with that one); may be empty for a caller whose records name neither
+    AddRowsFn add_rows;
+    DeltaRuleFn delta_rule;
 };
 
 // ---- records ---------------------------------------------------------------------------------------------------
@@ -207,6 +215,11 @@ enum RunnerOpKind {
                         // portion's first row is kept in state [slots, n]
     OP_ACTIVATE,        // out = activations(act(in)), in: float32 rows `ld` apart, n columns: the unit between the two products of a
                         // feed-forward without a gate
+    OP_ADD_ROWS,        // stream[t] += w[positions[t]] (fixed_row < 0) or w[fixed_row]: learned position vectors, a vector per pass;
+                        // w [k, n] of type w_dtype
+    OP_DELTA_RULE,      // in: float32 rows [q | k | v] (after their convolutions), SLOT_TMP: the projection's rows with the write
+                        // strength's and the decay's logits and the gate; S <- g S, S += k (beta (v - S^T k))^T, o = S^T q per head over
+                        // each request's rows and its state slot; out = rmsnorm(o) * vec * act(gate)
 };
 
 enum RunnerAct { RUNNER_ACT_NONE = 0, RUNNER_ACT_SILU = 1, RUNNER_ACT_GELU_TANH = 2, RUNNER_ACT_SIGMOID = 3, RUNNER_ACT_RELU = 4,
@@ -283,6 +296,19 @@ struct RunnerOp {
                                 // scores divided by their sum, multiplying the unit's output
     int into_stream;            // EXPERTS: 1 leaves SLOT_DELTA waiting to be added to the stream (by the next norm)
     float limit;                // EXPERTS: the clamp of RUNNER_ACT_SWISH_CLAMP
+    // ATTENTION, CONV_QKV: `window` < 0 means chunks of -window positions: a row sees the keys of its own chunk (jk_mask_lo).
+    // CONV_QKV: head_norm 2 norms every head of q and k BEFORE the rotation with the weights norm_q, norm_k [head_dim]; bias
+    // [ld] is added to the projection's columns.  LATENT_ATTENTION: window.  GATE_UP: act RUNNER_ACT_SWISH_CLAMP with limit.
+    // ---- what learned positions, queries through a latent, the delta rule and a gated shared expert add ------------------------
+    int fixed_row;              // ADD_ROWS: the table's row that every row gets; < 0: row positions[t]
+    int groups;                 // DELTA_RULE: heads of q and k (query head h reads group h / (heads / groups))
+    int b_off, a_off;           // DELTA_RULE: columns of the write strength's and the decay's logits in SLOT_TMP's rows
+    int q_rank;                 // LATENT_QKV: > 0: the queries pass a latent vector of q_rank elements at q_off, RMS-normed with norm_q
+                                // into out2 [T, q_rank]; the heads' queries are products of it (no per-head parts are split here)
+    float unit_eps;             // DELTA_RULE: q and k become x / sqrt(sum(x^2) + unit_eps)
+    const float *a_log, *dt_bias;       // DELTA_RULE: [heads]; g = exp(-exp(a_log) softplus(logit + dt_bias))
+    const float *router_bias;   // EXPERTS: [experts] added to the router's logits, or null
+    const float *gate_w;        // EXPERTS: [n] or null: what waits in SLOT_DELTA (add = 1) is multiplied by sigmoid(gate_w . in) per row
     const float *bonus;         // LINEAR_ATTENTION: [heads, head_dim]; a row then reads the state before its own decay, its own key
                                 // times the bonus: o = (S + diag(bonus) k v^T)^T q, then S = diag(a) S + k v^T
     // ATTENTION: cap > 0 caps the scores, s <- cap tanh(s / cap).

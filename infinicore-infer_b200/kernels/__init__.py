@@ -603,21 +603,21 @@ def layernorm(src: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     return out
 
 
-def glu(gate_up: torch.Tensor, out: torch.Tensor, act: int) -> torch.Tensor:
+def glu(gate_up: torch.Tensor, out: torch.Tensor, act: int, limit: float = 0.0) -> torch.Tensor:
     """out[t, c] = act(gate_up[t, c]) * gate_up[t, di + c]; gate_up float32."""
     _need(gate_up, "gate_up", torch.float32); _need(out, "out")
     ntok, di = out.shape
     if gate_up.shape != (ntok, 2 * di):
         raise KernelError(f"glu: gate_up {tuple(gate_up.shape)} for out {tuple(out.shape)}")
     lib = _build.load("mixers")
-    _check("mixers", lib.jk_glu(_ptr(gate_up), _ptr(out), _c_int(dtype_code(out.dtype)), _c_int(ntok), _c_int(di), _c_int(act), _stream()))
+    _check("mixers", lib.jk_glu(_ptr(gate_up), _ptr(out), _c_int(dtype_code(out.dtype)), _c_int(ntok), _c_int(di), _c_int(act), _c_float(limit), _stream()))
     return out
 
 
 def conv_qkv(u: torch.Tensor, offsets, heads: int, kv_heads: int, dk: int, dv: int, has_kv: bool, convs, taps: int, norms, eps: float,
              freq: Optional[torch.Tensor], rot_dims: int, tail: Optional[torch.Tensor], positions, row_req, req_start, slot_ids,
              block_table: Optional[torch.Tensor], page_size: int, q_out: torch.Tensor, k_pages=None, v_pages=None,
-             rot_half: bool = False, rot_mag: float = 1.0, head_norm: bool = False) -> torch.Tensor:
+             rot_half: bool = False, rot_mag: float = 1.0, head_norm=False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Short convolution, whole-projection RMS norm, pair rotation and cache write of fused float32 projections ``u``
     ``[T, ld]`` (columns ``offsets = (q, k, v)``); ``convs = (q, k, v)`` taps ``[channels, taps]`` or None each;
     ``norms = (q, k)`` weights or None each; ``tail [slots, taps - 1, channels]`` is read and moved forward.  ``rot_half``
@@ -632,7 +632,7 @@ def conv_qkv(u: torch.Tensor, offsets, heads: int, kv_heads: int, dk: int, dv: i
         _ptr(norms[0]), _ptr(norms[1]), _c_float(eps), _ptr(freq), _c_int(rot_dims), _ptr(tail), _ptr(positions), _ptr(row_req),
         _ptr(req_start), _ptr(slot_ids), _ptr(block_table), _c_int(block_table.shape[1] if block_table is not None else 0),
         _c_int(page_size), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _c_int(dtype_code(q_out.dtype)), _c_int(T), _c_int(nreq),
-        _c_int(1 if rot_half else 0), _c_float(rot_mag), _c_int(1 if head_norm else 0), _stream()))
+        _c_int(1 if rot_half else 0), _c_float(rot_mag), _c_int(int(head_norm)), _ptr(bias), _stream()))
     return q_out
 
 
@@ -718,15 +718,16 @@ def norm_add(delta: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: fl
 
 def latent_qkv(u: torch.Tensor, q_off: int, kv_off: int, heads: int, dn: int, dr: int, latent: int, rot_dims: int,
                freq: Optional[torch.Tensor], magnitude: float, norm_weight: torch.Tensor, eps: float, positions, row_req, block_table,
-               page_size: int, q_plain: torch.Tensor, q_full: torch.Tensor, pages: torch.Tensor) -> None:
+               page_size: int, q_plain: torch.Tensor, q_full: Optional[torch.Tensor], pages: torch.Tensor, q_norm: Optional[torch.Tensor] = None,
+               q_rank: int = 0) -> None:
     """Queries and cache rows of a latent attention from the fused float32 projection ``u`` (see csrc/blocks.cu)."""
-    _need(u, "u", torch.float32); _need(q_plain, "q_plain"); _need(q_full, "q_full"); _need(pages, "pages")
+    _need(u, "u", torch.float32); _need(q_plain, "q_plain"); _need(pages, "pages")
     lib = _build.load("blocks")
     _check("blocks", lib.jk_latent_qkv(
         _ptr(u), _c_int(u.shape[1]), _c_int(q_off), _c_int(kv_off), _c_int(heads), _c_int(dn), _c_int(dr), _c_int(latent), _c_int(rot_dims),
         _ptr(freq), _c_float(magnitude), _ptr(norm_weight), _c_float(eps), _ptr(positions), _ptr(row_req), _ptr(block_table),
         _c_int(block_table.shape[1]), _c_int(page_size), _ptr(q_plain), _ptr(q_full), _ptr(pages), _c_int(dtype_code(pages.dtype)),
-        _c_int(u.shape[0]), _stream()))
+        _c_int(u.shape[0]), _ptr(q_norm), _c_int(q_rank), _stream()))
 
 
 def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_head_stride: int, gate: Optional[torch.Tensor] = None,
@@ -741,7 +742,7 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_head_st
 
 
 def latent_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, positions, row_req, block_table, heads: int, latent: int,
-                     dr: int, scale: float, splits: int = 1, req_start: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     dr: int, scale: float, splits: int = 1, req_start: Optional[torch.Tensor] = None, window: int = 0) -> torch.Tensor:
     """Causal attention of ``heads`` query heads ``[T, heads, latent + dr]`` over the paged rows ``[pages, page, latent + dr]``;
     out ``[T, heads, latent]``.  ``splits`` > 1 cuts each row's keys into that many ranges.  With ``req_start`` (int32, the first
     row of each request and the row count) bfloat16 rows run on the tensor cores."""
@@ -754,7 +755,7 @@ def latent_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, po
     _check("blocks", lib.jk_latent_attention(_ptr(q), _ptr(pages), _ptr(out), _ptr(part), _c_int(dtype_code(q.dtype)), _ptr(positions),
                                              _ptr(row_req), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(pages.shape[-2]),
                                              _c_int(T), _c_int(heads), _c_int(latent), _c_int(dr), _c_float(scale), _c_int(splits), _ptr(req_start),
-                                             _c_int(req_start.numel() - 1 if req_start is not None else 0), _stream()))
+                                             _c_int(req_start.numel() - 1 if req_start is not None else 0), _c_int(window), _stream()))
     return out
 
 
@@ -786,7 +787,8 @@ def selective_scan(x: torch.Tensor, low: torch.Tensor, dt_rank: int, states: int
 
 
 def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, delta: torch.Tensor, add: bool,
-                   experts: int, top: int, act: int, score_form: int = 0, limit: float = 0.0) -> torch.Tensor:
+                   experts: int, top: int, act: int, score_form: int = 0, limit: float = 0.0, router_bias: Optional[torch.Tensor] = None,
+                   gate_w: Optional[torch.Tensor] = None) -> torch.Tensor:
     """delta (+)= sum over each row's ``top`` experts of largest sigmoid(router h) of expert(score * h); ``w_gate_up``
     ``[experts * 2 ff, d]`` (an expert's gate rows, then its up rows), ``w_down [experts * d, ff]``."""
     _need(h, "h"); _need(router, "router", torch.float32); _need(delta, "delta", torch.float32)
@@ -799,7 +801,8 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
     y = torch.empty(T * top, d, dtype=torch.float32, device=h.device)
     _check("blocks", lib.jk_routed_experts(_ptr(h), _ptr(router), _ptr(w_gate_up), _ptr(w_down), _ptr(delta), _c_int(1 if add else 0),
                                            _c_int(dtype_code(h.dtype)), _c_int(T), _c_int(d), _c_int(ff), _c_int(experts), _c_int(top),
-                                           _c_int(act), _ptr(route), _ptr(act_buf), _ptr(y), _c_int(score_form), _c_float(limit), _stream()))
+                                           _c_int(act), _ptr(route), _ptr(act_buf), _ptr(y), _c_int(score_form), _c_float(limit), _ptr(router_bias), _ptr(gate_w),
+                                           _stream()))
     return delta
 
 

@@ -19,10 +19,12 @@ from .sandwich_block import SandwichBlock
 from .reinject import Reinject
 from .mlp import MLP
 from .parallel_mixer import ParallelMixer
+from .step_vector import StepVector
+from .delta_rule import DeltaRule
 from .model import Model, cache_needs, model_manifest, state_needs
 
 __all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "ResidualStream", "Runtime", "StepContext", "Program",
            "ProgramRunner", "HostIO", "part_class", "register", "RMSNorm", "RotaryTables", "Attention", "SwiGLU",
            "PreNormBlock", "LayerNorm", "GLU", "LinearAttention", "ConvAttention", "PostNormBlock", "LatentAttention",
-           "SelectiveScan", "RoutedExperts", "SandwichBlock", "Reinject", "MLP", "ParallelMixer", "Model", "cache_needs", "model_manifest",
+           "SelectiveScan", "RoutedExperts", "SandwichBlock", "Reinject", "MLP", "ParallelMixer", "StepVector", "DeltaRule", "Model", "cache_needs", "model_manifest",
            "state_needs"]

@@ -49,6 +49,10 @@ class ConvAttention:
                 decls[name + spec.conv_suffix] = TensorDecl((n, spec.conv_taps), VECTOR, init="taps")
             if normed and spec.qk_norm:
                 decls[name + spec.norm_suffix] = TensorDecl((n,), VECTOR, init="ones")
+            elif normed and spec.head_norm == "before_rotation":
+                decls[name + spec.norm_suffix] = TensorDecl((spec.head_dim,), VECTOR, init="ones")
+            if spec.bias:
+                decls[name + spec.bias_suffix] = TensorDecl((n,), VECTOR, init="zeros")
         if spec.head_gate:
             decls[spec.gate_name] = TensorDecl((spec.num_heads, d))
         decls[spec.o_name] = TensorDecl((d, spec.num_heads * spec.v_head_dim))
@@ -56,7 +60,8 @@ class ConvAttention:
 
     @staticmethod
     def cache_need(spec):
-        return PagedKV(spec.num_kv_heads, spec.head_dim, spec.window,
+        # a chunked mask never looks further back than one chunk: the pages behind that are given back as for a window
+        return PagedKV(spec.num_kv_heads, spec.head_dim, spec.window or spec.chunk,
                        None if spec.v_head_dim == spec.head_dim else spec.v_head_dim,
                        keep_first=spec.keep_first if spec.window else 0)
 
@@ -75,7 +80,15 @@ class ConvAttention:
         self.w_o = weights.get(prefix + spec.o_name, MATRIX)
         get = lambda name: weights.get(prefix + name, VECTOR)
         self.conv = {n: get(n + spec.conv_suffix) for n, _, _ in proj} if spec.conv_taps else {}
-        self.norms = {n: get(n + spec.norm_suffix) for n, _, normed in proj if normed} if spec.qk_norm else {}
+        if spec.window and spec.chunk:
+            raise ValueError("an attention has a sliding window or chunks, not both")
+        if spec.head_norm == "before_rotation" and spec.qk_norm:
+            raise ValueError("a norm over the whole projection and one per head ahead of the rotation are not built together")
+        if spec.bias and (spec.conv_taps or spec.head_gate):
+            raise ValueError("biases beside a convolution or a gate per head are not built")
+        per_head = spec.qk_norm or spec.head_norm == "before_rotation"
+        self.norms = {n: get(n + spec.norm_suffix) for n, _, normed in proj if normed} if per_head else {}
+        self.bias = torch.cat([get(n + spec.bias_suffix) for n, _, _ in proj]).contiguous() if spec.bias else None
         self.freq, self.rot_mag = None, 1.0
         if spec.position is not None and spec.position.dims:
             p = spec.position
@@ -119,16 +132,17 @@ class ConvAttention:
                    conv_q=self.conv.get(s.q_name), conv_k=self.conv.get(s.k_name), conv_v=self.conv.get(s.v_name),
                    norm_q=self.norms.get(s.q_name), norm_k=self.norms.get(s.k_name), eps=s.qk_norm_eps, freq=self.freq, rot_dims=rot,
                    state=state, cache_group=view.group_index, k_pages=view.k_pages, v_pages=view.v_pages,
-                   num_pages=view.k_pages.shape[0], writes_cache=writes_cache, head_norm=s.head_norm, rot_mag=self.rot_mag,
+                   num_pages=view.k_pages.shape[0], writes_cache=writes_cache, rot_mag=self.rot_mag, bias=self.bias,
+                   head_norm=2 if s.head_norm == "before_rotation" else int(bool(s.head_norm)),
                    rot_half=self.freq is not None and s.position.layout == "halves"),
             record("attention", "q", "o", heads=s.num_heads, kv_heads=s.num_kv_heads, head_dim=s.head_dim, v_head_dim=s.v_head_dim,
-                   window=s.window or 0, softmax_scale=s.softmax_scale, cache_group=view.group_index, list_short=short,
+                   window=-int(s.chunk) if s.chunk else (s.window or 0), softmax_scale=s.softmax_scale, cache_group=view.group_index, list_short=short,
                    list_tiles=tiles, max_positions=program.max_blocks * program.page_size, k_pages=view.k_pages,
                    v_pages=view.v_pages, num_pages=view.k_pages.shape[0], sink=s.sink, gated=s.head_gate, ld=ld, g_off=g_off,
                    cap=float(s.score_cap or 0.0), keep_first=s.keep_first if s.window else 0),
             record("linear", "o", "delta", n=s.hidden_size, k=s.num_heads * s.v_head_dim, w=self.w_o) if into_stream is None else
             record("residual", "o", "x", n=s.hidden_size, k=s.num_heads * s.v_head_dim, w=self.w_o, scale=float(into_stream)),
-        ], keep=(self.w_in, self.w_o, self.conv, self.norms, self.freq, state, view.k_pages, view.v_pages))
+        ], keep=(self.w_in, self.w_o, self.conv, self.norms, self.freq, state, view.k_pages, view.v_pages, self.bias))
 
     def forward(self, h: torch.Tensor, ctx, view, writes_cache: bool = True, state_view=None) -> torch.Tensor:
         """The part alone: its own records over ``h``; float32 ``[T, hidden]``."""

@@ -21,6 +21,8 @@ def model_manifest(spec) -> Dict[str, TensorDecl]:
     the checkpoint has none the embedding is used (scripts/jiuge.py:182-191)."""
     out = {spec.embed_name: TensorDecl((spec.vocab_size, spec.hidden_size)),
            spec.lm_head_name: TensorDecl((spec.vocab_size, spec.hidden_size), optional=True)}
+    if spec.position_table_name:
+        out[spec.position_table_name] = TensorDecl((spec.position_rows, spec.hidden_size))
     for name, decl in part_class("norm", spec.final_norm).tensor_decls(spec.final_norm).items():
         out[spec.final_norm_prefix + name] = decl
     for i, layer in enumerate(spec.layers):
@@ -73,6 +75,11 @@ class Model:
             self.lm_head = weights.get(spec.lm_head_name, MATRIX)
         else:
             self.lm_head = self.embedding       # tied: one copy serves both ends
+        self.position_table = None
+        if spec.position_table_name:          # a learned vector per position, added to the embedding's output
+            self.position_table = weights.get(spec.position_table_name, MATRIX)
+            if spec.max_positions > self.position_table.shape[0]:
+                raise ValueError(f"sequences of up to {spec.max_positions} positions, but {spec.position_table_name} holds {self.position_table.shape[0]}")
         self.final_norm = part_class("norm", spec.final_norm)(spec.final_norm, weights,
                                                               spec.final_norm_prefix, runtime)
         self.layers = [part_class("block", layer)(layer, weights, spec.layer_prefix.format(i), runtime)
@@ -88,6 +95,8 @@ class Model:
     def weight_bytes_per_step(self) -> int:
         """Bytes of weights one decode step reads: every matrix of every run entry, the output matrix."""
         total = self.lm_head.numel() * self.lm_head.element_size()
+        if self.position_table is not None:
+            total += self.spec.hidden_size * self.position_table.element_size()
         for e in self.spec.order:
             total += getattr(self.layers[e.layer], "weight_bytes", lambda: 0)()
         total += sum(b.weight_bytes() for b in self.before if b is not None and hasattr(b, "weight_bytes"))
@@ -103,6 +112,10 @@ class Model:
         program.emit("jk_emit_embedding", ctypes.c_void_p(self.embedding.data_ptr()), ctypes.c_int(kernels.dtype_code(self.embedding.dtype)),
                      ctypes.c_int(spec.hidden_size), ctypes.c_float(spec.embed_scale), keep=(self.embedding,))
         hidden = spec.hidden_size
+        if self.position_table is not None:
+            from .program import record
+            program.emit_records([record("add_rows", "x", "x", n=hidden, k=self.position_table.shape[0], w=self.position_table,
+                                         w_dtype=kernels.dtype_code(self.position_table.dtype), fixed_row=-1)], keep=(self.position_table,))
         if any(getattr(b, "needs_embedding_output", False) for b in self.before):
             from .program import record
             program.emit_records([record("embed", None, "x0", n=hidden, w=self.embedding, w_dtype=kernels.dtype_code(self.embedding.dtype),

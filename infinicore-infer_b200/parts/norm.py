@@ -17,11 +17,13 @@ from .base import ResidualStream, register
 class RMSNorm:
     @staticmethod
     def tensor_decls(spec) -> Dict[str, TensorDecl]:
-        return {spec.weight_name: TensorDecl((spec.size,), VECTOR, init="ones")}
+        return {spec.weight_name: TensorDecl((spec.size,), VECTOR, init="zeros" if getattr(spec, "one_plus", False) else "ones")}
 
     def __init__(self, spec, weights, prefix: str, runtime):
         self.spec, self.runtime = spec, runtime
         self.weight = weights.get(prefix + spec.weight_name, VECTOR)
+        if getattr(spec, "one_plus", False):          # stored around zero: the factor is 1 + w, formed once in float32
+            self.weight = (self.weight.to(torch.float32) + 1.0).contiguous()
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

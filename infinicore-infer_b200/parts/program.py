@@ -29,12 +29,12 @@ SLOT = {name: i for i, name in enumerate(SLOTS)}
 OP_NAMES = {1: "embed", 2: "norm", 3: "qkv", 4: "attention", 5: "residual", 6: "gate_up", 7: "linear", 8: "cast",
             9: "layernorm", 10: "conv_qkv", 11: "linear_attention", 12: "norm_add", 13: "reinject", 14: "latent_qkv",
             15: "head_linear", 16: "latent_attention", 17: "causal_conv", 18: "selective_scan", 19: "experts", 20: "softcap",
-            21: "token_shift", 22: "activate"}
+            21: "token_shift", 22: "activate", 23: "add_rows", 24: "delta_rule"}
 OP = {name: kind for kind, name in OP_NAMES.items()}                                # RunnerOpKind
 ACT = {"none": 0, "silu": 1, "gelu_tanh": 2, "sigmoid": 3, "relu": 4, "gelu_erf": 5, "swish_clamp": 6, "tanh": 7}    # RunnerAct
-_MIXERS_OPS = (OP["cast"], OP["layernorm"], OP["conv_qkv"], OP["linear_attention"], OP["token_shift"], OP["activate"])
+_MIXERS_OPS = (OP["cast"], OP["layernorm"], OP["conv_qkv"], OP["linear_attention"], OP["token_shift"], OP["activate"], OP["delta_rule"])
 _BLOCKS_OPS = tuple(OP[n] for n in ("norm_add", "reinject", "latent_qkv", "head_linear", "latent_attention", "causal_conv",
-                                    "selective_scan", "experts", "softcap"))
+                                    "selective_scan", "experts", "softcap", "add_rows"))
 MAX_GROUPS = 8
 MAX_LISTS = 8
 
@@ -58,7 +58,11 @@ class RunnerOp(ctypes.Structure):
                 # what a window attention with kept first keys, a token-shifted recurrence and softmax-routed experts add
                 + [(n, _i) for n in ("keep_first", "rot_half", "head_norm", "in_part", "out_off", "decay_form", "rank_act", "score_form",
                                      "into_stream")]
-                + [("limit", _f), ("bonus", _p)])
+                + [("limit", _f)]
+                # what learned positions, queries through a latent, the delta rule and a gated shared expert add
+                + [(n, _i) for n in ("fixed_row", "groups", "b_off", "a_off", "q_rank")]
+                + [("unit_eps", _f)]
+                + [(n, _p) for n in ("a_log", "dt_bias", "router_bias", "gate_w", "bonus")])
 
 
 class Routing(ctypes.Structure):
@@ -91,7 +95,7 @@ class _Fns(ctypes.Structure):
         "linear_small_qkv_norm", "argmax", "sample", "err_sampling", "layernorm", "cast_rows", "glu", "conv_qkv", "linear_scan",
         "norm_gate", "token_shift", "act_rows", "err_mixers", "norm_add", "concat_cast", "add_bias_rows", "latent_qkv", "head_linear", "latent_attention",
         "latent_attention_scratch", "causal_conv", "selective_scan", "routed_experts", "routed_experts_workspace",
-        "routed_experts_launches", "softcap", "err_blocks", "linear_small_parts", "linear_small_parts_supports")]
+        "routed_experts_launches", "softcap", "err_blocks", "linear_small_parts", "linear_small_parts_supports", "add_rows", "delta_rule")]
 
 
 def _addr(lib, name: str) -> int:
@@ -150,7 +154,8 @@ def runner_lib(gemm_tcgen05: bool = False, attention_tcgen05: bool = False, mixe
         routed_experts_launches=get("blocks", "jk_routed_experts_launches"), softcap=get("blocks", "jk_softcap"),
         err_blocks=get("blocks", "jk_blocks_last_error"),
         linear_small_parts=get("linear_small", "jk_linear_small_parts"),
-        linear_small_parts_supports=get("linear_small", "jk_linear_small_parts_supports"))
+        linear_small_parts_supports=get("linear_small", "jk_linear_small_parts_supports"),
+        add_rows=get("blocks", "jk_add_rows"), delta_rule=get("mixers", "jk_delta_rule"))
     if lib.jk_runner_bind(ctypes.byref(fns)):
         from ..kernels import KernelError
         raise KernelError(lib.jk_runner_last_error().decode(errors="replace"))

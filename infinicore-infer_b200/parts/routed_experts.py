@@ -7,7 +7,8 @@ device, so a step never waits for the host; the experts' products run over those
 
 The other form of scores (``score_form`` "softmax_renorm"): softmax over all experts, the chosen ones' scores divided by
 their sum, multiplying the units' outputs; and the other unit (``act`` "swish_clamp"): clamped sums,
-g sigmoid(1.702 g) (u + 1).
+g sigmoid(1.702 g) (u + 1).  The router may have a bias, and the shared unit's output a gate per row, sigmoid(w . h), which
+the kernel that adds the experts' sum applies to what it adds to.
 """
 from __future__ import annotations
 
@@ -26,6 +27,10 @@ class RoutedExperts:
     def tensor_decls(spec) -> Dict[str, TensorDecl]:
         d, f = spec.hidden_size, spec.expert_size
         decls = {spec.router_name: TensorDecl((spec.num_experts, d), VECTOR)}
+        if spec.router_bias:
+            decls[spec.router_name + spec.bias_suffix] = TensorDecl((spec.num_experts,), VECTOR, init="zeros")
+        if spec.shared_gate_name:
+            decls[spec.shared_prefix + spec.shared_gate_name] = TensorDecl((1, d), VECTOR)
         for e in range(spec.num_experts):
             p = spec.expert_prefix.format(e)
             decls[p + spec.gate_name] = TensorDecl((f, d))
@@ -47,6 +52,10 @@ class RoutedExperts:
         if not 1 <= spec.top <= spec.num_experts:
             raise ValueError(f"{spec.top} of {spec.num_experts} experts")
         self.router = weights.get(prefix + spec.router_name, VECTOR)
+        self.router_bias = weights.get(prefix + spec.router_name + spec.bias_suffix, VECTOR) if spec.router_bias else None
+        if spec.shared_gate_name and spec.shared is None:
+            raise ValueError("a gate on a shared unit that the layer does not have")
+        self.shared_gate = weights.get(prefix + spec.shared_prefix + spec.shared_gate_name, VECTOR) if spec.shared_gate_name else None
         names = [prefix + spec.expert_prefix.format(e) for e in range(spec.num_experts)]
         self.w_gate_up = weights.get_rows([p + n for p in names for n in (spec.gate_name, spec.up_name)], MATRIX)
         self.w_down = weights.get_rows([p + spec.down_name for p in names], MATRIX)
@@ -75,8 +84,9 @@ class RoutedExperts:
         program.emit_records([
             record("experts", "h", "delta", n=s.hidden_size, experts=s.num_experts, top=s.top, ff=s.expert_size, vec=self.router,
                    w=self.w_gate_up, w3=self.w_down, add=self.shared is not None, act=ACT[s.act], limit=float(s.limit),
-                   score_form=1 if s.score_form == "softmax_renorm" else 0, into_stream=into_stream),
-        ], keep=(self.router, self.w_gate_up, self.w_down))
+                   score_form=1 if s.score_form == "softmax_renorm" else 0, into_stream=into_stream, router_bias=self.router_bias,
+                   gate_w=self.shared_gate),
+        ], keep=(self.router, self.w_gate_up, self.w_down, self.router_bias, self.shared_gate))
 
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
         """The part alone: its own records over ``h``; float32 ``[T, hidden]``."""
