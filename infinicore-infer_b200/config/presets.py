@@ -84,4 +84,17 @@ PRESETS: Dict[str, Preset] = {
                 "right": {"heads": 4, "dim": 8, "rank": 6}, "left_scale": 1.0, "right_scale": 1.0},
              "mlp": None},
         ]), 0.1, 0.05, 16),
+    # a small Fapenex: learned positions, a span of two layers that runs twice, one layer of each mixer (a delta rule, chunked
+    # attention with partial stretched rotation, windowed latent attention), routed experts with and without the shared unit
+    "fapenex-tiny": Preset(dict(
+        architecture="Fapenex", vocab=320, width=96, max_positions=256, norm={"eps": 1e-5}, logit_scale=1.5, logit_softcap=20.0,
+        loop={"start": 1, "stop": 3, "times": 2}, layers=[
+            {"type": "delta", "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "conv": 4},
+             "mlp": {"kind": "moe", "router": {"experts": 6, "top": 2}, "expert": {"ff": 48, "limit": 1.5}, "shared": {"ff": 64, "limit": 2.0}}},
+            {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 16, "scale": 0.3, "mask": {"size": 24},
+                                            "rot": {"base": 1e4, "dims": 16, "scaling": {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 1.0}}},
+             "mlp": {"kind": "moe", "router": {"experts": 4, "top": 1}, "expert": {"ff": 80, "limit": 1.0}}},
+            {"type": "latent_attention", "mixer": {"heads": 3, "dim": 16, "vdim": 24, "kv_rank": 32, "q_rank": 40, "scale": 0.25,
+                                                   "mask": {"size": 17}}, "mlp": None},
+        ]), 0.1, 0.05, 16),
 }

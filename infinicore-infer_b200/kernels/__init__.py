@@ -845,3 +845,29 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, topk: torch.Tensor, 
 
 def build_all(verbose: bool = True):
     return _build.build_all(verbose)
+
+
+def add_rows(x: torch.Tensor, table: torch.Tensor, index: Optional[torch.Tensor], row: int = -1) -> torch.Tensor:
+    """x[t] += table[index[t]] (``index`` int32 per row), or table[row] for every row when ``index`` is None; x float32, the
+    table float32 or bfloat16."""
+    _need(x, "x", torch.float32); _need(table, "table")
+    lib = _build.load("blocks")
+    _check("blocks", lib.jk_add_rows(_ptr(x), _ptr(table), _c_int(dtype_code(table.dtype)), _c_int(table.shape[0]), _ptr(index), _c_int(row),
+                                     _c_int(x.shape[0]), _c_int(x.shape[1]), _stream()))
+    return x
+
+
+def delta_rule(c: torch.Tensor, offsets, u: torch.Tensor, b_off: int, a_off: int, a_log: torch.Tensor, dt_bias: torch.Tensor, heads: int,
+               groups: int, dk: int, dv: int, q_scale: float, unit_eps: float, state: torch.Tensor, req_start: torch.Tensor,
+               slot_ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """The gated delta rule over each request's rows (csrc/mixers.cu): ``c`` float32 rows with q, k, v at the columns
+    ``offsets`` (after their convolutions), ``u`` float32 rows with the write strength's logits at ``b_off`` and the decay's at
+    ``a_off``; from and into ``state [slots, heads, dk, dv]``; ``out`` float32 ``[T, heads * dv]``."""
+    for t, n in ((c, "c"), (u, "u"), (a_log, "a_log"), (dt_bias, "dt_bias"), (state, "state"), (out, "out")):
+        _need(t, n, torch.float32)
+    lib = _build.load("mixers")
+    _check("mixers", lib.jk_delta_rule(_ptr(c), _c_int(c.shape[1]), _c_int(offsets[0]), _c_int(offsets[1]), _c_int(offsets[2]), _ptr(u),
+                                       _c_int(u.shape[1]), _c_int(b_off), _c_int(a_off), _ptr(a_log), _ptr(dt_bias), _c_int(heads), _c_int(groups),
+                                       _c_int(dk), _c_int(dv), _c_float(q_scale), _c_float(unit_eps), _ptr(state), _ptr(req_start),
+                                       _ptr(slot_ids), _c_int(req_start.numel() - 1), _ptr(out), _stream()))
+    return out

@@ -23,6 +23,12 @@ import math
 import numpy as np
 
 
+def operand(a):
+    """Every operand of a matrix product passes here.  The identity; a test that wants to know what 16-bit operands alone do
+    to a model's logits replaces it by a rounding."""
+    return a
+
+
 def rms_unit(x, eps):
     return x / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + eps)
 
@@ -114,14 +120,14 @@ def latent_attention(h, m, w, p, eps, positions=None):
     T = h.shape[0]
     H, d, dv = int(m["heads"]), int(m["dim"]), int(m["vdim"])
     positions = np.arange(T) if positions is None else np.asarray(positions)
-    cq = norm_plain(h @ w[p + "dq"].T, w[p + "dq.norm"], eps)
-    q = (cq @ w[p + "uq"].T).reshape(T, H, d)
-    c = norm_plain(h @ w[p + "dkv"].T, w[p + "dkv.norm"], eps)
-    k = (c @ w[p + "uk"].T).reshape(T, H, d)
-    v = (c @ w[p + "uv"].T).reshape(T, H, dv)
+    cq = operand(norm_plain(h @ w[p + "dq"].T, w[p + "dq.norm"], eps))
+    q = operand((cq @ w[p + "uq"].T).reshape(T, H, d))
+    c = operand(norm_plain(h @ w[p + "dkv"].T, w[p + "dkv.norm"], eps))
+    k = operand((c @ w[p + "uk"].T).reshape(T, H, d))
+    v = operand((c @ w[p + "uv"].T).reshape(T, H, dv))
     see = visibility(positions, sees_window, int(m["mask"]["size"]))
     out = masked_softmax_attention(q, k, v, float(m["scale"]), see, sink=False)
-    return out.reshape(T, H * dv) @ w[p + "o"].T
+    return operand(out.reshape(T, H * dv)) @ w[p + "o"].T
 
 
 def chunk_attention(h, m, w, p, eps, positions=None):
@@ -135,8 +141,8 @@ def chunk_attention(h, m, w, p, eps, positions=None):
     if m.get("rot") and int(m["rot"].get("dims") or 0):
         q, k = rotate_half(q, positions, m["rot"]), rotate_half(k, positions, m["rot"])
     see = visibility(positions, sees_chunk, int(m["mask"]["size"]))
-    out = masked_softmax_attention(q, k, v, float(m["scale"]), see, sink=True)
-    return out.reshape(T, H * dv) @ w[p + "o"].T
+    out = masked_softmax_attention(operand(q), operand(k), operand(v), float(m["scale"]), see, sink=True)
+    return operand(out.reshape(T, H * dv)) @ w[p + "o"].T
 
 
 def short_conv(u, taps, before=None):
@@ -183,14 +189,14 @@ def delta_mixer(h, m, w, p, eps):
     g = np.exp(-np.exp(w[p + "A_log"]) * softplus(h @ w[p + "a"].T + w[p + "dt_bias"]))
     o, _ = delta_recurrence(q, k, v, g, beta)
     o = rms_unit(o, eps) * w[p + "norm"] * silu(h @ w[p + "g"].T).reshape(T, H, dv)
-    return o.reshape(T, H * dv) @ w[p + "o"].T
+    return operand(o.reshape(T, H * dv)) @ w[p + "o"].T
 
 
 # ---- feed-forward ------------------------------------------------------------------------------------------------------
 def clamped_unit(h, w, p, limit):
     g = np.minimum(h @ w[p + "gate"].T, limit)
     u = np.clip(h @ w[p + "up"].T, -limit, limit)
-    return (g * sigmoid(1.702 * g) * (u + 1.0)) @ w[p + "down"].T
+    return operand(g * sigmoid(1.702 * g) * (u + 1.0)) @ w[p + "down"].T
 
 
 def router_logits(h, w, p):
@@ -233,10 +239,10 @@ MIXERS = {"latent_attention": latent_attention, "delta": delta_mixer, "attention
 
 
 def layer(x, spec, w, p, eps, margins=None):
-    h = norm_one_plus(x, w[p + "norm1"], eps)
+    h = operand(norm_one_plus(x, w[p + "norm1"], eps))
     x = x + norm_one_plus(MIXERS[spec["type"]](h, spec["mixer"], w, p + "mix.", eps), w[p + "norm1b"], eps)
     if spec.get("mlp") is not None:
-        h = norm_one_plus(x, w[p + "norm2"], eps)
+        h = operand(norm_one_plus(x, w[p + "norm2"], eps))
         x = x + norm_one_plus(experts_ff(h, spec["mlp"], w, p + "mlp.", margins), w[p + "norm2b"], eps)
     return x
 
@@ -265,6 +271,6 @@ def forward(cfg, w, tokens, streams=None, margins=None):
         x = layer(x, cfg["layers"][i], w, f"l{i}.", eps, margins)
         if streams is not None:
             streams.append(x.copy())
-    logits = norm_one_plus(x, w["final.norm"], eps) @ w["embed"].T * float(cfg.get("logit_scale") or 1.0)
+    logits = operand(norm_one_plus(x, w["final.norm"], eps)) @ w["embed"].T * float(cfg.get("logit_scale") or 1.0)
     cap = cfg.get("logit_softcap")
     return float(cap) * np.tanh(logits / float(cap)) if cap else logits
