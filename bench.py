@@ -288,6 +288,24 @@ def vipovik_shape(width, ff, heads, kv_heads, dim, vocab, window):
             "layers": [{"type": "parallel", "mixer": mixer, "mlp": mlp} for mlp in (dense, moe, dense, moe, dense, moe)]}
 
 
+def fapenex_shape(width, ff, heads, kv_heads, dim, vocab, window):
+    """Six layers, eight layer runs (the second and third layer run twice): a gated delta rule with heads of ``dim`` x ``dim``
+    behind convolutions of four taps; attention with grouped heads of ``dim``, biases, a norm per head, half of each head
+    rotated with stretched frequencies, chunks of ``window`` positions and a sink; latent attention with heads of ``dim``, a
+    latent vector of 4 dim, queries through a latent of 3/4 width, a window of ``window``.  Every layer has eight clamped
+    experts of ff / 4 of which a row takes two, and a shared one with a gate per row.  Learned positions."""
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": ff // 4, "limit": 7.0}, "shared": {"ff": ff // 4, "limit": 7.0}}
+    delta = {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "conv": 4}, "mlp": moe}
+    att = {"type": "attention", "mlp": moe,
+           "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
+                     "rot": {"base": 1e4, "dims": dim // 2, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}}
+    lat = {"type": "latent_attention", "mlp": moe,
+           "mixer": {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": 4 * dim, "q_rank": 3 * width // 4, "scale": dim ** -0.5,
+                     "mask": {"size": window}}}
+    return {"architecture": "Fapenex", "norm": {"eps": 1e-5}, "vocab": vocab, "width": width, "max_positions": 8192, "logit_scale": 1.0,
+            "logit_softcap": 30.0, "loop": {"start": 1, "stop": 3, "times": 2}, "layers": [delta, att, lat, lat, delta, att]}
+
+
 def decoder_shape(width, ff, heads, kv_heads, dim, vocab, layers=8):
     return dict(model_type="llama", num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv_heads,
                 head_dim=dim, intermediate_size=ff, vocab_size=vocab, max_position_embeddings=4096, rms_norm_eps=1e-5,
@@ -305,7 +323,7 @@ def record_cost(op, T, B, context, decode, page_bytes):
     if kind == "gate_up":
         return 2 * 2 * op.n * op.k + 2 * T * op.k + 2 * T * op.n, 2.0 * T * 2 * op.n * op.k
     if kind == "attention":
-        reach = min(context, op.window) if op.window else context
+        reach = min(context, abs(op.window)) if op.window else context      # a negative window: chunks of that many positions
         keys = B * reach if decode else T       # cached rows that are read at least once
         seen = (B * reach) if decode else sum(min(t + 1, reach) for t in range(T))
         return keys * op.kv_heads * (op.head_dim + dv) * 2 + 2 * T * op.heads * (op.head_dim + dv), 2.0 * seen * op.heads * (op.head_dim + dv)
@@ -332,13 +350,19 @@ def record_cost(op, T, B, context, decode, page_bytes):
         return 2 * op.heads * op.n * op.k + 2 * T * op.heads * (op.k + op.n), 2.0 * T * op.heads * op.n * op.k
     if kind == "latent_attention":
         width = op.rank + op.rot_width
-        keys = B * context if decode else T
-        seen = (B * context) if decode else T * (T + 1) // 2
+        reach = min(context, op.window) if op.window else context
+        keys = B * reach if decode else T
+        seen = (B * reach) if decode else sum(min(t + 1, reach) for t in range(T))
         return keys * width * 2 + 2 * T * op.heads * (width + op.rank), 2.0 * seen * op.heads * (width + op.rank)
     if kind == "causal_conv":
         return T * op.n * (4 + 4 + 2), 2.0 * T * op.n * op.taps
     if kind == "selective_scan":
         return T * op.n * (4 + 4 + 2) + 4 * T * (op.rank + 2 * op.k) + 2 * B * op.n * op.k * 4, T * op.n * (6.0 * op.k + 2.0 * op.rank)
+    if kind == "delta_rule":
+        state = B * op.heads * op.head_dim * dv * 4 * 2
+        return state + 4 * T * (op.ld + 2 * op.heads + op.heads * dv) + (4 + 2) * T * op.heads * dv, 6.0 * T * op.heads * op.head_dim * dv
+    if kind == "add_rows":
+        return T * op.n * (4 + 4 + 2), 0.0
     if kind == "experts":
         used = min(op.experts, T * op.top)
         return used * 3 * op.n * op.ff * 2 + T * op.n * (2 + 4) + T * op.top * (op.ff * 4 + op.n * 8), 2.0 * T * op.top * 3 * op.n * op.ff
@@ -346,12 +370,12 @@ def record_cost(op, T, B, context, decode, page_bytes):
 
 
 def run_design(args):
-    """Prefill and decode of another design (Sitelorn, Vunelix, Vipovik) at layer sizes of real models beside the decoder (llama graph) of
-    the same width, feed-forward, heads and layer count (Vipovik: also beside Sitelorn, the design closest to it), and every kind
+    """Prefill and decode of another design (Sitelorn, Vunelix, Vipovik, Fapenex) at layer sizes of real models beside the decoder (llama graph) of
+    the same width, feed-forward, heads and layer count (Vipovik: also beside Sitelorn, Fapenex: also beside Vunelix, the designs closest to them), and every kind
     of launch record of each timed alone against its roofline.  Prints one JSON line of its own kind; the default benchmark is
     untouched."""
     import torch
-    from infinicore_infer_b200.config import MiniCPMConfig, SitelornConfig, VipovikConfig, VunelixConfig
+    from infinicore_infer_b200.config import FapenexConfig, MiniCPMConfig, SitelornConfig, VipovikConfig, VunelixConfig
     from infinicore_infer_b200.engine import Engine, StepEntry
     from infinicore_infer_b200.parts import model_manifest
     from infinicore_infer_b200.parts.program import OP_NAMES
@@ -369,8 +393,12 @@ def run_design(args):
         for size in args.design_sizes.split(","):
             width, ff, heads, kv_heads, dim, vocab = DESIGN_SIZES[size]
             block = out["sizes"][size] = {"width": width, "ff": ff, "heads": heads, "kv_heads": kv_heads, "head_dim": dim, "layers": 8}
-            for which in (args.design, "sitelorn", "decoder") if args.design == "vipovik" else (args.design, "decoder"):
-                if which == "vipovik":
+            beside = {"vipovik": ("sitelorn",), "fapenex": ("vunelix",)}.get(args.design, ())
+            for which in (args.design,) + beside + ("decoder",):
+                if which == "fapenex":
+                    cfg = FapenexConfig.from_dict(fapenex_shape(width, ff, heads, kv_heads, dim, vocab, args.design_window),
+                                                  max_tokens=max(4096, context + page))
+                elif which == "vipovik":
                     cfg = VipovikConfig.from_dict(vipovik_shape(width, ff, heads, kv_heads, dim, vocab, args.design_window),
                                                   max_tokens=max(4096, context + page))
                 elif which == "vunelix":
@@ -456,7 +484,7 @@ def run_design(args):
                             nbytes, flops = record_cost(op, rows, nreq, pos + 1 if dec else T, dec, page)
                             row[phase + "_us"] = round(us, 2)
                             mem_frac = nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"]
-                            peak_f = F32_FMA_TFLOPS if OP_NAMES.get(op.kind) in ("linear_attention", "selective_scan", "causal_conv") else peaks["bf16_tflops"]
+                            peak_f = F32_FMA_TFLOPS if OP_NAMES.get(op.kind) in ("linear_attention", "selective_scan", "causal_conv", "delta_rule") else peaks["bf16_tflops"]
                             flop_frac = flops / (us * 1e-6) / 1e12 / peak_f
                             row[phase + "_frac"] = round(max(mem_frac, flop_frac), 4)
                             row[phase + "_bound"] = "memory" if mem_frac >= flop_frac else "compute"
@@ -488,7 +516,7 @@ def main():
                     help="run a few steps between cudaProfilerStart/Stop (for ncu --profile-from-start off) and exit")
     ap.add_argument("--shape", default="2b", choices=["2b", "1b", "8b"],
                     help="layer sizes: 2b is the headline configuration; the others are for profiles and side measurements")
-    ap.add_argument("--design", default=None, choices=["sitelorn", "vunelix", "vipovik"],
+    ap.add_argument("--design", default=None, choices=["sitelorn", "vunelix", "vipovik", "fapenex"],
                     help="instead of the benchmark: prefill and decode of this design at real layer sizes beside the decoder of equal size")
     ap.add_argument("--design-sizes", default="2k,4k", help="comma-separated names of " + ", ".join(sorted(DESIGN_SIZES)))
     ap.add_argument("--design-prompt", type=int, default=2048)

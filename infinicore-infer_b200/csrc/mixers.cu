@@ -1198,17 +1198,22 @@ JK_EXPORT int jk_act_rows(const float *u, int ld, void *out, int dtype, int T, i
 // The gated delta rule: per request and head, over the request's rows in order,
 //     S <- g_t S;   w_t = beta_t (v_t - S^T k_t);   S <- S + k_t w_t^T;   o_t = S^T q_t          S [dk, dv], float32
 // so a row's read-out sees its own write.  q and k come as float32 rows `c` (after their convolutions and activations),
-// one head per key/value group (query head h reads group h / (heads / groups)), and are made unit vectors here,
+// one head per key/value group (query head h reads group h / (heads / groups)), and are made unit vectors,
 // x / sqrt(sum(x^2) + unit_eps), q also times q_scale; v likewise from `c`, one head per query head.  The write strength
 // beta_t = sigmoid(u[t, b_off + h]) and the decay g_t = exp(-exp(A_log[h]) softplus(u[t, a_off + h] + dt_bias[h])) are
-// formed here in float32 from the float32 projection rows `u`.  S lives in state[slot, h] between steps.
+// formed in float32 from the float32 projection rows `u`.  S lives in state[slot, h] between steps.
 //
-// A block owns DR_COLS value columns of one (request, head); DR_LANES neighbouring lanes share a column and keep the
-// key channels part, part + DR_LANES, ... of it in registers (NPER each).  Rows pass shared memory DR_ROWS at a time: the
-// block norms q and k (a warp a row), stages its columns of v, the rows' beta and g.  A row then costs two sums over the
-// lanes of a column (S^T k before the write, S^T q after it) and 3 NPER multiply-adds a thread.
+// Two kernels.  delta_prep (a block a row) does what does not depend on the state, once per row instead of once per block
+// of the scan: the unit vectors of every group, laid out as the scan's lanes read them, and per head (g, beta, k . q).
+// delta_scan: a block owns DR_COLS value columns of one (request, head); DR_LANES neighbouring lanes share a column and
+// keep the key channels part, part + DR_LANES, ... of it in registers (NPER each).  The prepared rows arrive DR_ROWS at a
+// time by 16-byte asynchronous copies into two buffers that take turns, each lane's channels in 16-byte pieces on banks of
+// their own.  Both sums over a column's lanes that a row needs are taken from the state BEFORE the row's write, so they
+// run side by side and a row costs one round of shuffles:
+//     a = S^T k,  b = S^T q  (old S);   w = beta (v - g a);   o = g b + w (k . q);   S <- g S + k w^T
+// which is the recurrence above with o = (g S + k w^T)^T q multiplied out.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int DR_LANES = 8, DR_COLS = 16, DR_THREADS = DR_LANES * DR_COLS, DR_ROWS = 16;
+constexpr int DR_LANES = 8, DR_COLS = 16, DR_THREADS = DR_LANES * DR_COLS, DR_ROWS = 32;
 
 struct DeltaArgs {
     const float *c;             // [T, ld_c]: q at q_off (groups * dk), k at k_off (groups * dk), v at v_off (heads * dv)
@@ -1221,98 +1226,162 @@ struct DeltaArgs {
     float *state;               // [slots, heads, dk, dv]
     const int *req_start, *slot_ids;
     float *out;                 // [T, heads * dv]
+    float *prep;                // [T, groups, 2, DR_LANES * nper] unit k then q, channel i at (i % DR_LANES) * nper + i / DR_LANES;
+    float *scal;                // [T, heads, 4]: g, beta, k . q, 0
+    int nper;
 };
 
-template <int NPER>
-__global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(DeltaArgs a) {
+// floats of scratch that T rows need
+JK_EXPORT long long jk_delta_rule_scratch_floats(int T, int heads, int groups, int dk) {
+    const int per = (dk + DR_LANES - 1) / DR_LANES, nper = per <= 4 ? 4 : (per <= 8 ? 8 : (per <= 16 ? 16 : 32));
+    return (long long)T * ((long long)groups * 2 * DR_LANES * nper + 4LL * heads);
+}
+
+__global__ void __launch_bounds__(128) delta_prep_kernel(DeltaArgs a) {
     pdl_trigger();
     pdl_wait();
-    constexpr int KP = NPER * DR_LANES;         // key channels, padded: the padding holds zeros
-    __shared__ float ks[DR_ROWS][KP], qs[DR_ROWS][KP], vs[DR_ROWS][DR_COLS], gs[DR_ROWS], bs[DR_ROWS];
-    const int h = blockIdx.x, req = blockIdx.y, col0 = blockIdx.z * DR_COLS;
-    const int group = h / (a.heads / a.groups);
-    const int part = threadIdx.x % DR_LANES, cl = threadIdx.x / DR_LANES, col = col0 + cl;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const bool live = col < a.dv;
-    const int first = a.req_start[req], n = a.req_start[req + 1] - first;
-    float *S = a.state + (((size_t)a.slot_ids[req] * a.heads + h) * a.dk) * a.dv;
-    float s[NPER];
-#pragma unroll
-    for (int r = 0; r < NPER; ++r) {
-        const int i = part + DR_LANES * r;
-        s[r] = (live && i < a.dk) ? S[(size_t)i * a.dv + col] : 0.f;
-    }
-    const float rate = expf(a.A_log[h]), bias = a.dt_bias[h];
-    for (int r0 = 0; r0 < n; r0 += DR_ROWS) {
-        const int nr = min(DR_ROWS, n - r0);
-        __syncthreads();        // the rows before are done with
-        for (int r = warp; r < nr; r += DR_THREADS / 32) {
-            const float *row = a.c + (size_t)(first + r0 + r) * a.ld_c;
-            const float *kr = row + a.k_off + (size_t)group * a.dk, *qr = row + a.q_off + (size_t)group * a.dk;
-            float sk = 0.f, sq = 0.f;
-            for (int i = lane; i < a.dk; i += 32) { sk = fmaf(kr[i], kr[i], sk); sq = fmaf(qr[i], qr[i], sq); }
-            const float ik = 1.f / sqrtf(warp_sum(sk) + a.unit_eps), iq = a.q_scale / sqrtf(warp_sum(sq) + a.unit_eps);
-            for (int i = lane; i < KP; i += 32) {
-                ks[r][i] = i < a.dk ? kr[i] * ik : 0.f;
-                qs[r][i] = i < a.dk ? qr[i] * iq : 0.f;
+    __shared__ float kq_s[64];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, KW = DR_LANES * a.nper;
+    const float *row = a.c + (size_t)t * a.ld_c;
+    for (int g0 = 0; g0 < a.groups; g0 += 64) {
+        for (int grp = g0 + warp; grp < min(a.groups, g0 + 64); grp += 4) {
+            const float *kr = row + a.k_off + (size_t)grp * a.dk, *qr = row + a.q_off + (size_t)grp * a.dk;
+            float sk = 0.f, sq = 0.f, kq = 0.f;
+            for (int i = lane; i < a.dk; i += 32) { sk = fmaf(kr[i], kr[i], sk); sq = fmaf(qr[i], qr[i], sq); kq = fmaf(kr[i], qr[i], kq); }
+            sk = warp_sum(sk); sq = warp_sum(sq); kq = warp_sum(kq);
+            const float ik = 1.f / sqrtf(sk + a.unit_eps), iq = a.q_scale / sqrtf(sq + a.unit_eps);
+            float *dst = a.prep + ((size_t)t * a.groups + grp) * 2 * KW;
+            for (int i = lane; i < KW; i += 32) {
+                const int at = (i % DR_LANES) * a.nper + i / DR_LANES;
+                dst[at] = i < a.dk ? kr[i] * ik : 0.f;
+                dst[KW + at] = i < a.dk ? qr[i] * iq : 0.f;
             }
-        }
-        for (int i = threadIdx.x; i < nr * DR_COLS; i += DR_THREADS) {
-            const int r = i / DR_COLS, cc = i % DR_COLS;
-            vs[r][cc] = col0 + cc < a.dv ? a.c[(size_t)(first + r0 + r) * a.ld_c + a.v_off + (size_t)h * a.dv + col0 + cc] : 0.f;
-        }
-        if (threadIdx.x < nr) {
-            const float *urow = a.u + (size_t)(first + r0 + threadIdx.x) * a.ld_u;
-            const float z = urow[a.a_off + h] + bias;
-            const float sp = z > 20.f ? z : log1pf(expf(z));
-            gs[threadIdx.x] = expf(-rate * sp);
-            bs[threadIdx.x] = sigmoid_f(urow[a.b_off + h]);
+            if (lane == 0) kq_s[grp - g0] = kq * ik * iq;
         }
         __syncthreads();
-        for (int r = 0; r < nr; ++r) {
-            const float g = gs[r], beta = bs[r];
-            float kv = 0.f;
-#pragma unroll
-            for (int j = 0; j < NPER; ++j) kv = fmaf(s[j], ks[r][part + DR_LANES * j], kv);
-            kv += __shfl_xor_sync(0xffffffffu, kv, 1);
-            kv += __shfl_xor_sync(0xffffffffu, kv, 2);
-            kv += __shfl_xor_sync(0xffffffffu, kv, 4);
-            const float w = beta * (vs[r][cl] - g * kv);
-            float o = 0.f;
-#pragma unroll
-            for (int j = 0; j < NPER; ++j) {
-                s[j] = fmaf(ks[r][part + DR_LANES * j], w, g * s[j]);
-                o = fmaf(s[j], qs[r][part + DR_LANES * j], o);
-            }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
-            if (part == 0 && live) a.out[(size_t)(first + r0 + r) * a.heads * a.dv + (size_t)h * a.dv + col] = o;
+        const int per_group = a.heads / a.groups;
+        for (int h = g0 * per_group + threadIdx.x; h < min(a.groups, g0 + 64) * per_group; h += blockDim.x) {
+            const float *urow = a.u + (size_t)t * a.ld_u;
+            const float z = urow[a.a_off + h] + a.dt_bias[h];
+            const float sp = z > 20.f ? z : log1pf(expf(z));
+            float4 v;
+            v.x = expf(-expf(a.A_log[h]) * sp);
+            v.y = sigmoid_f(urow[a.b_off + h]);
+            v.z = kq_s[h / per_group - g0];
+            v.w = 0.f;
+            *reinterpret_cast<float4 *>(a.scal + ((size_t)t * a.heads + h) * 4) = v;
         }
-    }
-#pragma unroll
-    for (int r = 0; r < NPER; ++r) {
-        const int i = part + DR_LANES * r;
-        if (live && i < a.dk) S[(size_t)i * a.dv + col] = s[r];
+        __syncthreads();
     }
 }
 
+__device__ __forceinline__ void dr_copy4(float *dst, const float *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void dr_copy16(float *dst, const float *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+template <int NPER>
+__global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(DeltaArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int LP = NPER + 4, KP = DR_LANES * LP;        // a lane's channels, padded so that the lanes' pieces fall on different banks
+    constexpr int ROWF = 2 * KP + DR_COLS + 4;              // floats a row takes in shared memory: k, q, the block's values, (g, beta, k . q, -)
+    constexpr int KW = DR_LANES * NPER, PIECES = KW / 4;
+    extern __shared__ __align__(16) float dr_smem[];        // [2][DR_ROWS][ROWF]
+    const int h = blockIdx.x, req = blockIdx.y, col0 = blockIdx.z * DR_COLS;
+    const int group = h / (a.heads / a.groups);
+    const int part = threadIdx.x % DR_LANES, cl = threadIdx.x / DR_LANES, col = col0 + cl;
+    const bool live = col < a.dv;
+    const int first = a.req_start[req], n = a.req_start[req + 1] - first;
+    float *S = a.state + (((size_t)a.slot_ids[req] * a.heads + h) * a.dk) * a.dv;
+    const size_t voff = a.v_off + (size_t)h * a.dv + col0;
+    auto fetch = [&](int r0, float *buf) {
+        const int nr = min(DR_ROWS, n - r0);
+        for (int i = threadIdx.x; i < nr * 2 * PIECES; i += DR_THREADS) {
+            const int r = i / (2 * PIECES), p = i % (2 * PIECES), which = p / PIECES, pp = p % PIECES;
+            const float *src = a.prep + ((size_t)(first + r0 + r) * a.groups + group) * 2 * KW + which * KW + pp * 4;
+            dr_copy16(buf + r * ROWF + which * KP + (pp / (NPER / 4)) * LP + (pp % (NPER / 4)) * 4, src);
+        }
+        for (int i = threadIdx.x; i < nr * DR_COLS; i += DR_THREADS) {
+            const int r = i / DR_COLS, cc = i % DR_COLS;
+            if (col0 + cc < a.dv) dr_copy4(buf + r * ROWF + 2 * KP + cc, a.c + (size_t)(first + r0 + r) * a.ld_c + voff + cc);
+        }
+        if (threadIdx.x < nr) dr_copy16(buf + threadIdx.x * ROWF + 2 * KP + DR_COLS, a.scal + ((size_t)(first + r0 + threadIdx.x) * a.heads + h) * 4);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    float s[NPER];
+#pragma unroll
+    for (int j = 0; j < NPER; ++j) {
+        const int i = part + DR_LANES * j;
+        s[j] = (live && i < a.dk) ? S[(size_t)i * a.dv + col] : 0.f;
+    }
+    if (n > 0) fetch(0, dr_smem);
+    int turn = 0;
+    for (int r0 = 0; r0 < n; r0 += DR_ROWS, turn ^= 1) {
+        const int nr = min(DR_ROWS, n - r0);
+        const float *buf = dr_smem + turn * DR_ROWS * ROWF;
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads();        // this chunk's rows are there, and everyone is done with the other buffer
+        if (r0 + DR_ROWS < n) fetch(r0 + DR_ROWS, dr_smem + (turn ^ 1) * DR_ROWS * ROWF);
+        float *orow = a.out + (size_t)(first + r0) * a.heads * a.dv + (size_t)h * a.dv + col;
+        for (int r = 0; r < nr; ++r) {
+            const float *rowp = buf + r * ROWF;
+            const float4 row = *reinterpret_cast<const float4 *>(rowp + 2 * KP + DR_COLS);      // g, beta, k . q
+            const float v = live ? rowp[2 * KP + cl] : 0.f;
+            const float *kp = rowp + part * LP, *qp = rowp + KP + part * LP;
+            float kk[NPER];
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < NPER; j += 4) {
+                const float4 k4 = *reinterpret_cast<const float4 *>(kp + j), q4 = *reinterpret_cast<const float4 *>(qp + j);
+                kk[j] = k4.x; kk[j + 1] = k4.y; kk[j + 2] = k4.z; kk[j + 3] = k4.w;
+                a0 = fmaf(s[j], k4.x, a0); a1 = fmaf(s[j + 1], k4.y, a1); a0 = fmaf(s[j + 2], k4.z, a0); a1 = fmaf(s[j + 3], k4.w, a1);
+                b0 = fmaf(s[j], q4.x, b0); b1 = fmaf(s[j + 1], q4.y, b1); b0 = fmaf(s[j + 2], q4.z, b0); b1 = fmaf(s[j + 3], q4.w, b1);
+            }
+            float sk = a0 + a1, sq = b0 + b1;
+            sk += __shfl_xor_sync(0xffffffffu, sk, 1); sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+            sk += __shfl_xor_sync(0xffffffffu, sk, 2); sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+            sk += __shfl_xor_sync(0xffffffffu, sk, 4); sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+            const float w = row.y * (v - row.x * sk);
+#pragma unroll
+            for (int j = 0; j < NPER; ++j) s[j] = fmaf(kk[j], w, row.x * s[j]);
+            if (part == 0 && live) orow[(size_t)r * a.heads * a.dv] = fmaf(w, row.z, row.x * sq);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NPER; ++j) {
+        const int i = part + DR_LANES * j;
+        if (live && i < a.dk) S[(size_t)i * a.dv + col] = s[j];
+    }
+}
+
+// `scratch`: jk_delta_rule_scratch_floats(T, ...) floats
 JK_EXPORT int jk_delta_rule(const float *c, int ld_c, int q_off, int k_off, int v_off, const float *u, int ld_u, int b_off, int a_off,
                             const float *A_log, const float *dt_bias, int heads, int groups, int dk, int dv, float q_scale, float unit_eps,
-                            float *state, const int *req_start, const int *slot_ids, int nreq, float *out, cudaStream_t stream) {
-    if (nreq == 0) return JK_OK;
-    JK_REQUIRE(c && u && A_log && dt_bias && state && req_start && slot_ids && out, "delta_rule: an argument is missing");
+                            float *state, const int *req_start, const int *slot_ids, int nreq, float *out, float *scratch, int T,
+                            cudaStream_t stream) {
+    if (nreq == 0 || T == 0) return JK_OK;
+    JK_REQUIRE(c && u && A_log && dt_bias && state && req_start && slot_ids && out && scratch, "delta_rule: an argument is missing");
     JK_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0 && dk > 0 && dv > 0, "delta_rule: %d heads on %d groups, sizes %d and %d", heads, groups, dk, dv);
     JK_REQUIRE(dk <= 32 * DR_LANES, "delta_rule: key heads of %d exceed %d", dk, 32 * DR_LANES);
     JK_REQUIRE(nreq <= 65535 && (dv + DR_COLS - 1) / DR_COLS <= 65535, "delta_rule: %d requests exceed one launch", nreq);
+    JK_REQUIRE((uintptr_t)scratch % 16 == 0, "delta_rule: the scratch does not start on a 16-byte boundary");
+    const int per = (dk + DR_LANES - 1) / DR_LANES, nper = per <= 4 ? 4 : (per <= 8 ? 8 : (per <= 16 ? 16 : 32));
     DeltaArgs a{c, ld_c, q_off, k_off, v_off, u, ld_u, b_off, a_off, A_log, dt_bias, heads, groups, dk, dv, q_scale, unit_eps, state, req_start,
-                slot_ids, out};
+                slot_ids, out, scratch, scratch + (size_t)T * groups * 2 * DR_LANES * nper, nper};
+    jk_launch(delta_prep_kernel, dim3(T), dim3(128), 0, stream, a);
+    JK_CHECK_LAUNCH("delta_prep");
     const dim3 grid(heads, nreq, (dv + DR_COLS - 1) / DR_COLS);
-    const int per = (dk + DR_LANES - 1) / DR_LANES;
-    if (per <= 4) jk_launch(delta_rule_kernel<4>, grid, dim3(DR_THREADS), 0, stream, a);
-    else if (per <= 8) jk_launch(delta_rule_kernel<8>, grid, dim3(DR_THREADS), 0, stream, a);
-    else if (per <= 16) jk_launch(delta_rule_kernel<16>, grid, dim3(DR_THREADS), 0, stream, a);
-    else jk_launch(delta_rule_kernel<32>, grid, dim3(DR_THREADS), 0, stream, a);
-    JK_CHECK_LAUNCH("delta_rule");
+#define LAUNCH(NPER)                                                                                                                         \
+    do {                                                                                                                                     \
+        const size_t smem = (size_t)2 * DR_ROWS * (2 * DR_LANES * (NPER + 4) + DR_COLS + 4) * sizeof(float);                                 \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<NPER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+        jk_launch(delta_scan_kernel<NPER>, grid, dim3(DR_THREADS), smem, stream, a);                                                         \
+    } while (0)
+    if (nper == 4) LAUNCH(4); else if (nper == 8) LAUNCH(8); else if (nper == 16) LAUNCH(16); else LAUNCH(32);
+#undef LAUNCH
+    JK_CHECK_LAUNCH("delta_scan");
     return JK_OK;
 }

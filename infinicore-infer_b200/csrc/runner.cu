@@ -593,11 +593,12 @@ int run_head_linear(Run &r, const RunnerOp &op) {
     return JK_OK;
 }
 
-// How many ranges the keys of a row are cut into: steps of few rows fill the SMs with ranges of at least 256 keys.
-int latent_splits(int T, int heads, int context, int sms) {
+// How many ranges the keys of a row are cut into: steps of few rows fill the SMs with ranges of at least 256 keys (128
+// where a window bounds a row's keys: a launch's time is that of one range, and a window leaves few ranges of 256).
+int latent_splits(int T, int heads, int context, int sms, int least = 256) {
     if (T > 16) return 1;
     const int blocks = T * ((heads + 7) / 8);
-    const int want = (2 * sms + blocks - 1) / blocks, by_length = (context + 255) / 256;
+    const int want = (2 * sms + blocks - 1) / blocks, by_length = (context + least - 1) / least;
     return std::max(1, std::min(std::min(want, by_length), 64));
 }
 
@@ -611,7 +612,7 @@ int run_latent_attention(Run &r, const RunnerOp &op) {
     JK_REQUIRE(table != nullptr, "runner: a latent attention reads the cache of group %d, whose block table the step lacks", op.cache_group);
     int reach = r.st.context > 0 ? r.st.context : op.max_positions;
     if (op.window > 0) reach = std::min(reach, op.window);
-    const int splits = latent_splits(T, H, reach, r.env.routing.sms);
+    const int splits = latent_splits(T, H, reach, r.env.routing.sms, op.window > 0 ? 128 : 256);
     void *part = nullptr;
     if (splits > 1)
         if (int rc = r.slot(SLOT_DECODE, 4 * g_fns.latent_attention_scratch(T, H, op.rank, splits), &part, "the ranges of a latent attention")) return rc;
@@ -710,17 +711,21 @@ int run_add_rows(Run &r, const RunnerOp &op) {
 // (the write strength's logit at b_off + h, the decay's at a_off + h, the gate at g_off)
 int run_delta_rule(Run &r, const RunnerOp &op) {
     if (int rc = need_mixers("a delta rule")) return rc;
-    JK_REQUIRE(g_fns.delta_rule != nullptr, "runner: a delta rule needs its kernel, which was not bound");
+    JK_REQUIRE(g_fns.delta_rule != nullptr && g_fns.delta_rule_scratch != nullptr, "runner: a delta rule needs its kernel, which was not bound");
     const int T = r.st.ntok, dv = op.v_head_dim;
     void *c, *u, *mix, *out;
     if (int rc = r.slot(op.in_slot, 4LL * T * op.ld, &c, "the convolved q/k/v")) return rc;
     if (int rc = r.slot(SLOT_TMP, 4LL * T * op.r_off, &u, "the projection that holds a delta rule's logits and gate")) return rc;
-    if (int rc = r.slot(SLOT_SCAN, 4LL * T * op.heads * dv, &mix, "a recurrence's output")) return rc;
+    // the slot of the recurrences' scratch holds the output before its norm, then what the rows' preparation leaves
+    const long long o_floats = ((long long)T * op.heads * dv + 3) / 4 * 4;
+    const long long prep_floats = g_fns.delta_rule_scratch(T, op.heads, op.groups, op.head_dim);
+    if (int rc = r.slot(SLOT_SCAN, 4 * (o_floats + prep_floats), &mix, "a recurrence's output and its prepared rows")) return rc;
     if (int rc = r.slot(op.out_slot, (long long)r.elem() * T * op.heads * dv, &out, "a delta rule's output")) return rc;
     JK_REQUIRE(r.st.slot_ids != nullptr && op.state != nullptr, "runner: a recurrence without its state slots");
     RUN(mixers, g_fns.delta_rule((const float *)c, op.ld, op.q_off, op.k_off, op.v_off, (const float *)u, op.r_off, op.b_off, op.a_off, op.a_log,
                                  op.dt_bias, op.heads, op.groups, op.head_dim, dv, op.q_scale, op.unit_eps, op.state, r.st.req_start,
-                                 r.st.slot_ids, r.st.nreq, (float *)mix, r.stream));
+                                 r.st.slot_ids, r.st.nreq, (float *)mix, (float *)mix + o_floats, T, r.stream));
+    ++g_launches;       // the rows' preparation
     RUN(mixers, g_fns.norm_gate((const float *)mix, (const float *)u, op.r_off, op.g_off, op.vec, op.eps, op.heads, dv, op.per_head_norm,
                                 op.gate_act, out, r.env.dtype, T, r.stream));
     return JK_OK;
@@ -923,7 +928,7 @@ JK_EXPORT int jk_runner_slot_bytes(const RunnerEnv *env, const RunnerOp *ops, in
                 need(op.in_slot, e * rows * op.heads * (op.rank + op.rot_width)); need(op.out_slot, e * rows * op.heads * op.rank);
                 long long worst = 0;
                 for (int n = 1; n <= 16 && n <= max_rows; ++n)
-                    worst = std::max(worst, (long long)n * op.heads * latent_splits(n, op.heads, op.max_positions, env->routing.sms) * (op.rank + 2));
+                    worst = std::max(worst, (long long)n * op.heads * latent_splits(n, op.heads, op.max_positions, env->routing.sms, 128) * (op.rank + 2));
                 need(SLOT_DECODE, 4 * worst);
                 break;
             }
@@ -945,7 +950,9 @@ JK_EXPORT int jk_runner_slot_bytes(const RunnerEnv *env, const RunnerOp *ops, in
             case OP_ADD_ROWS: need(SLOT_X, 4 * rows * op.n); break;
             case OP_DELTA_RULE: {
                 const long long width = (long long)op.heads * op.v_head_dim;
-                need(op.in_slot, 4 * rows * op.ld); need(SLOT_TMP, 4 * rows * op.r_off); need(SLOT_SCAN, 4 * rows * width);
+                const long long per = (op.head_dim + 7) / 8, nper = per <= 4 ? 4 : (per <= 8 ? 8 : (per <= 16 ? 16 : 32));
+                need(op.in_slot, 4 * rows * op.ld); need(SLOT_TMP, 4 * rows * op.r_off);
+                need(SLOT_SCAN, 4 * ((rows * width + 3) / 4 * 4 + rows * (op.groups * 2 * 8 * nper + 4LL * op.heads)));
                 need(op.out_slot, e * rows * width);
                 break;
             }

@@ -86,7 +86,8 @@ typedef int (*SoftcapFn)(float *, float, long long, cudaStream_t);
 typedef int (*AddRowsFn)(float *, const void *, int, int, const int *, int, int, int, cudaStream_t);
 // csrc/mixers.cu
 typedef int (*DeltaRuleFn)(const float *, int, int, int, int, const float *, int, int, int, const float *, const float *, int, int, int, int,
-                           float, float, float *, const int *, const int *, int, float *, cudaStream_t);
+                           float, float, float *, const int *, const int *, int, float *, float *, int, cudaStream_t);
+typedef long long (*DeltaScratchFn)(int, int, int, int);
 typedef int (*ArgmaxFn)(const float *, long long, int, int, int *, void *, cudaStream_t);
 typedef int (*SampleFn)(const float *, long long, int, int, const float *, const int *, const float *, const float *, int *,
                         cudaStream_t);
@@ -155,6 +156,7 @@ struct RunnerFns {
     // bound with that one); may be empty for a caller whose records name neither
     AddRowsFn add_rows;
     DeltaRuleFn delta_rule;
+    DeltaScratchFn delta_rule_scratch;
 };
 
 // ---- records ---------------------------------------------------------------------------------------------------

@@ -866,8 +866,11 @@ def delta_rule(c: torch.Tensor, offsets, u: torch.Tensor, b_off: int, a_off: int
     for t, n in ((c, "c"), (u, "u"), (a_log, "a_log"), (dt_bias, "dt_bias"), (state, "state"), (out, "out")):
         _need(t, n, torch.float32)
     lib = _build.load("mixers")
+    lib.jk_delta_rule_scratch_floats.restype = ctypes.c_longlong
+    scratch = torch.empty(int(lib.jk_delta_rule_scratch_floats(_c_int(c.shape[0]), _c_int(heads), _c_int(groups), _c_int(dk))) + 4,
+                          dtype=torch.float32, device=c.device)
     _check("mixers", lib.jk_delta_rule(_ptr(c), _c_int(c.shape[1]), _c_int(offsets[0]), _c_int(offsets[1]), _c_int(offsets[2]), _ptr(u),
                                        _c_int(u.shape[1]), _c_int(b_off), _c_int(a_off), _ptr(a_log), _ptr(dt_bias), _c_int(heads), _c_int(groups),
                                        _c_int(dk), _c_int(dv), _c_float(q_scale), _c_float(unit_eps), _ptr(state), _ptr(req_start),
-                                       _ptr(slot_ids), _c_int(req_start.numel() - 1), _ptr(out), _stream()))
+                                       _ptr(slot_ids), _c_int(req_start.numel() - 1), _ptr(out), _ptr(scratch), _c_int(c.shape[0]), _stream()))
     return out

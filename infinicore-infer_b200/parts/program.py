@@ -95,7 +95,7 @@ class _Fns(ctypes.Structure):
         "linear_small_qkv_norm", "argmax", "sample", "err_sampling", "layernorm", "cast_rows", "glu", "conv_qkv", "linear_scan",
         "norm_gate", "token_shift", "act_rows", "err_mixers", "norm_add", "concat_cast", "add_bias_rows", "latent_qkv", "head_linear", "latent_attention",
         "latent_attention_scratch", "causal_conv", "selective_scan", "routed_experts", "routed_experts_workspace",
-        "routed_experts_launches", "softcap", "err_blocks", "linear_small_parts", "linear_small_parts_supports", "add_rows", "delta_rule")]
+        "routed_experts_launches", "softcap", "err_blocks", "linear_small_parts", "linear_small_parts_supports", "add_rows", "delta_rule", "delta_rule_scratch")]
 
 
 def _addr(lib, name: str) -> int:
@@ -155,7 +155,7 @@ def runner_lib(gemm_tcgen05: bool = False, attention_tcgen05: bool = False, mixe
         err_blocks=get("blocks", "jk_blocks_last_error"),
         linear_small_parts=get("linear_small", "jk_linear_small_parts"),
         linear_small_parts_supports=get("linear_small", "jk_linear_small_parts_supports"),
-        add_rows=get("blocks", "jk_add_rows"), delta_rule=get("mixers", "jk_delta_rule"))
+        add_rows=get("blocks", "jk_add_rows"), delta_rule=get("mixers", "jk_delta_rule"), delta_rule_scratch=get("mixers", "jk_delta_rule_scratch_floats"))
     if lib.jk_runner_bind(ctypes.byref(fns)):
         from ..kernels import KernelError
         raise KernelError(lib.jk_runner_last_error().decode(errors="replace"))
