@@ -286,7 +286,9 @@ def chunk_edge_case(T, H, G, dk, dv, chunk, seed, bf16):
     """Queries, keys and values in which, for chosen rows i, head 0 scores the last key of the chunk before (just outside)
     above the first key of the row's own chunk (just inside) above all others, and head 1 scores a key far back, in an
     earlier chunk, above everything: a border that is one off in either direction, or chunks counted from elsewhere than
-    position 0, moves the row's output from one value to another."""
+    position 0, moves the row's output from one value to another.  And the last row of every chunk scores, with its last
+    head, the chunk's SECOND key above everything: a key as far back as the mask allows, among all the others, decides that
+    row (``far`` lists (row, key))."""
     g = torch.Generator().manual_seed(seed)
     q = torch.randn(T, H, dk, generator=g, dtype=F)
     k = 0.3 * torch.randn(T, G, dk, generator=g, dtype=F)
@@ -298,9 +300,22 @@ def chunk_edge_case(T, H, G, dk, dv, chunk, seed, bf16):
         k[start - 1, 0] = 14.0 * unit
         k[start, 0] = 9.0 * unit
         q[i, 1] = q[i, 0]
+    far = []
+    for start in range(0, T, chunk):              # the last head reads the last key head
+        last = min(start + chunk, T) - 1
+        if last - start >= 8:
+            k[start + 1, G - 1] = 16.0 * q[last, H - 1] / (q[last, H - 1] @ q[last, H - 1])
+            far.append((last, start + 1))
     if bf16:
         q, k, v = (t.to(torch.bfloat16).double() for t in (q, k, v))
+    chunk_edge_case.far = far
     return q, k, v, rows
+
+
+def far_keys_decide(want, v, far, G):
+    """The rows that were given a far key do read its value, almost alone."""
+    for row, key in far:
+        assert np.abs(want[row, -1] - v[key, G - 1].numpy()).max() < 0.05, f"row {row} does not rest on key {key}"
 
 
 def plain_chunks(q, k, v, chunk, positions, shift=0, sink=True):
@@ -317,6 +332,7 @@ def test_chunk_borders_and_the_sink_of_the_row_attention(dtype, chunk, page):
     T, H, G, dk, dv = 150, 4, 2, 24, 40
     q, k, v, rows = chunk_edge_case(T, H, G, dk, dv, chunk, chunk, dt == torch.bfloat16)
     want = plain_chunks(q, k, v, chunk, np.arange(T))
+    far_keys_decide(want, v, chunk_edge_case.far, G)
     for other in (plain_chunks(q, k, v, chunk, np.arange(T), shift=1), plain_chunks(q, k, v, chunk, np.arange(T), shift=-1),
                   plain_chunks(q, k, v, chunk, np.arange(T), sink=False)):
         assert np.abs(other - want)[rows].max() > 0.05       # the inputs do tell a border that is one off, and a lost sink
@@ -327,7 +343,7 @@ def test_chunk_borders_and_the_sink_of_the_row_attention(dtype, chunk, page):
     tol = 2e-5 if dt == torch.float32 else 3e-2
     err = np.abs(out.double().cpu().numpy() - want).max()
     assert err <= tol, f"prompt rows differ by {err}"
-    for i in rows[-4:] + [0, chunk - 1, chunk, chunk + 1]:       # the same rows one by one, as a decode step sees them
+    for i in rows[-4:] + [0, chunk - 1, chunk, chunk + 1] + [row for row, _ in chunk_edge_case.far]:       # the same rows one by one, as a decode step sees them
         one = torch.empty(1, H, dv, dtype=dt, device=dev)
         K.attention_rows(q[i:i + 1].to(dt).to(dev).contiguous(), kp, vp, one, pos[i:i + 1], torch.zeros(1, dtype=torch.int32, device=dev), table,
                          1, H, 1.0, -chunk, sink=True)
@@ -345,6 +361,8 @@ def test_chunk_borders_on_the_tensor_cores(dh, chunk):
     T, H, G, page = 333, 4, 2, 16
     q, k, v, rows = chunk_edge_case(T, H, G, dh, dh, chunk, chunk + dh, True)
     want = plain_chunks(q, k, v, chunk, np.arange(T))
+    far_keys_decide(want, v, chunk_edge_case.far, G)
+    rows = rows + [row for row, _ in chunk_edge_case.far]
     kp, vp, table = paged(k, v, page, dev, dt)
     qd = q.to(dt).to(dev).contiguous()
     kernels = [("legacy tiles", K.attention_prefill)]
@@ -433,10 +451,18 @@ def test_window_edges_of_the_latent_attention(dtype, H, R, window, page):
     for i in rows:
         unit = q[i, 0] / (q[i, 0] @ q[i, 0])
         c[i - window], c[i - window + 1] = 14.0 * unit, 9.0 * unit
+    far = []
+    if window >= T:                               # every key is seen: the last rows' last head rests on the second key, far back
+        for i in (T - 1, T - 2):
+            q[i, H - 1] = q[T - 1, H - 1]
+            far.append(i)
+        c[1] = 16.0 * q[T - 1, H - 1] / (q[T - 1, H - 1] @ q[T - 1, H - 1])
     if dt == torch.bfloat16:
         q, c = q.to(dt).double(), c.to(dt).double()
     see = plain.visibility(np.arange(T), plain.sees_window, window)
     want = plain.masked_softmax_attention(q.numpy(), c.numpy()[:, None], c.numpy()[:, None], 1.0, see, sink=False)
+    for i in far:
+        assert np.abs(want[i, -1] - c[1].numpy()).max() < 0.05 * np.abs(c[1].numpy()).max()
     for w2 in (window - 1, window + 1):
         other = plain.masked_softmax_attention(q.numpy(), c.numpy()[:, None], c.numpy()[:, None], 1.0,
                                                plain.visibility(np.arange(T), plain.sees_window, w2), sink=False)
@@ -454,7 +480,7 @@ def test_window_edges_of_the_latent_attention(dtype, H, R, window, page):
                                req_start=req_start if with_tiles else None, window=window)
             err = np.abs(out.double().cpu().numpy() - want[start:]).max()
             assert err <= tol, f"rows from {start} (tiles {with_tiles}): {err}"
-    for i in rows[-3:] + [0, min(window, T) - 1, min(window, T - 1)]:
+    for i in rows[-3:] + far + [0, min(window, T) - 1, min(window, T - 1)]:
         for splits in (1, 4):
             one = torch.empty(1, H, R, dtype=dt, device=dev)
             p1 = torch.tensor([i], dtype=torch.int32, device=dev)
