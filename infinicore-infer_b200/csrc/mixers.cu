@@ -1211,7 +1211,10 @@ JK_EXPORT int jk_act_rows(const float *u, int ld, void *out, int dtype, int T, i
 // their own.  Both sums over a column's lanes that a row needs are taken from the state BEFORE the row's write, so they
 // run side by side and a row costs one round of shuffles:
 //     a = S^T k,  b = S^T q  (old S);   w = beta (v - g a);   o = g b + w (k . q);   S <- g S + k w^T
-// which is the recurrence above with o = (g S + k w^T)^T q multiplied out.
+// which is the recurrence above with o = (g S + k w^T)^T q multiplied out.  Two rows share a round the same way: the sums of
+// row t + 1 against the state after row t are those against the state before row t, times g_t, plus w_t (k_t . k_(t+1)) and
+// w_t (k_t . q_(t+1)); delta_prep leaves those two products of neighbouring rows with row t + 1, and the state takes both
+// rows' writes at once, S <- g_(t+1) g_t S + g_(t+1) k_t w_t^T + k_(t+1) w_(t+1)^T.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int DR_LANES = 8, DR_COLS = 16, DR_THREADS = DR_LANES * DR_COLS, DR_ROWS = 32;
 
@@ -1227,36 +1230,40 @@ struct DeltaArgs {
     const int *req_start, *slot_ids;
     float *out;                 // [T, heads * dv]
     float *prep;                // [T, groups, 2, DR_LANES * nper] unit k then q, channel i at (i % DR_LANES) * nper + i / DR_LANES;
-    float *scal;                // [T, heads, 4]: g, beta, k . q, 0
+    float *scal;                // [T, heads, 8]: g, beta, k . q, 0; then k_(t-1) . k_t, k_(t-1) . q_t (unit vectors; row t - 1 of the step), 0, 0
     int nper;
 };
 
 // floats of scratch that T rows need
 JK_EXPORT long long jk_delta_rule_scratch_floats(int T, int heads, int groups, int dk) {
     const int per = (dk + DR_LANES - 1) / DR_LANES, nper = per <= 4 ? 4 : (per <= 8 ? 8 : (per <= 16 ? 16 : 32));
-    return (long long)T * ((long long)groups * 2 * DR_LANES * nper + 4LL * heads);
+    return (long long)T * ((long long)groups * 2 * DR_LANES * nper + 8LL * heads);
 }
 
 __global__ void __launch_bounds__(128) delta_prep_kernel(DeltaArgs a) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float kq_s[64];
+    __shared__ float kq_s[64], kk_prev_s[64], kq_prev_s[64];
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, KW = DR_LANES * a.nper;
     const float *row = a.c + (size_t)t * a.ld_c;
     for (int g0 = 0; g0 < a.groups; g0 += 64) {
         for (int grp = g0 + warp; grp < min(a.groups, g0 + 64); grp += 4) {
             const float *kr = row + a.k_off + (size_t)grp * a.dk, *qr = row + a.q_off + (size_t)grp * a.dk;
-            float sk = 0.f, sq = 0.f, kq = 0.f;
+            float sk = 0.f, sq = 0.f, kq = 0.f, sp = 0.f, pk = 0.f, pq = 0.f;
             for (int i = lane; i < a.dk; i += 32) { sk = fmaf(kr[i], kr[i], sk); sq = fmaf(qr[i], qr[i], sq); kq = fmaf(kr[i], qr[i], kq); }
-            sk = warp_sum(sk); sq = warp_sum(sq); kq = warp_sum(kq);
-            const float ik = 1.f / sqrtf(sk + a.unit_eps), iq = a.q_scale / sqrtf(sq + a.unit_eps);
+            if (t > 0) {        // the row before (of the same request whenever the scan pairs the two)
+                const float *pr = kr - a.ld_c;
+                for (int i = lane; i < a.dk; i += 32) { sp = fmaf(pr[i], pr[i], sp); pk = fmaf(pr[i], kr[i], pk); pq = fmaf(pr[i], qr[i], pq); }
+            }
+            sk = warp_sum(sk); sq = warp_sum(sq); kq = warp_sum(kq); sp = warp_sum(sp); pk = warp_sum(pk); pq = warp_sum(pq);
+            const float ik = 1.f / sqrtf(sk + a.unit_eps), iq = a.q_scale / sqrtf(sq + a.unit_eps), ip = 1.f / sqrtf(sp + a.unit_eps);
             float *dst = a.prep + ((size_t)t * a.groups + grp) * 2 * KW;
             for (int i = lane; i < KW; i += 32) {
                 const int at = (i % DR_LANES) * a.nper + i / DR_LANES;
                 dst[at] = i < a.dk ? kr[i] * ik : 0.f;
                 dst[KW + at] = i < a.dk ? qr[i] * iq : 0.f;
             }
-            if (lane == 0) kq_s[grp - g0] = kq * ik * iq;
+            if (lane == 0) { kq_s[grp - g0] = kq * ik * iq; kk_prev_s[grp - g0] = pk * ip * ik; kq_prev_s[grp - g0] = pq * ip * iq; }
         }
         __syncthreads();
         const int per_group = a.heads / a.groups;
@@ -1269,7 +1276,8 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(DeltaArgs a) {
             v.y = sigmoid_f(urow[a.b_off + h]);
             v.z = kq_s[h / per_group - g0];
             v.w = 0.f;
-            *reinterpret_cast<float4 *>(a.scal + ((size_t)t * a.heads + h) * 4) = v;
+            *reinterpret_cast<float4 *>(a.scal + ((size_t)t * a.heads + h) * 8) = v;
+            *reinterpret_cast<float4 *>(a.scal + ((size_t)t * a.heads + h) * 8 + 4) = make_float4(kk_prev_s[h / per_group - g0], kq_prev_s[h / per_group - g0], 0.f, 0.f);
         }
         __syncthreads();
     }
@@ -1287,7 +1295,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(DeltaArgs a) {
     pdl_trigger();
     pdl_wait();
     constexpr int LP = NPER + 4, KP = DR_LANES * LP;        // a lane's channels, padded so that the lanes' pieces fall on different banks
-    constexpr int ROWF = 2 * KP + DR_COLS + 4;              // floats a row takes in shared memory: k, q, the block's values, (g, beta, k . q, -)
+    constexpr int ROWF = 2 * KP + DR_COLS + 8;              // floats a row takes in shared memory: k, q, the block's values, the row's eight numbers
     constexpr int KW = DR_LANES * NPER, PIECES = KW / 4;
     extern __shared__ __align__(16) float dr_smem[];        // [2][DR_ROWS][ROWF]
     const int h = blockIdx.x, req = blockIdx.y, col0 = blockIdx.z * DR_COLS;
@@ -1308,7 +1316,9 @@ __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(DeltaArgs a) {
             const int r = i / DR_COLS, cc = i % DR_COLS;
             if (col0 + cc < a.dv) dr_copy4(buf + r * ROWF + 2 * KP + cc, a.c + (size_t)(first + r0 + r) * a.ld_c + voff + cc);
         }
-        if (threadIdx.x < nr) dr_copy16(buf + threadIdx.x * ROWF + 2 * KP + DR_COLS, a.scal + ((size_t)(first + r0 + threadIdx.x) * a.heads + h) * 4);
+        if (threadIdx.x < 2 * nr)
+            dr_copy16(buf + (threadIdx.x >> 1) * ROWF + 2 * KP + DR_COLS + 4 * (threadIdx.x & 1),
+                      a.scal + ((size_t)(first + r0 + (threadIdx.x >> 1)) * a.heads + h) * 8 + 4 * (threadIdx.x & 1));
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
     float s[NPER];
@@ -1326,7 +1336,46 @@ __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(DeltaArgs a) {
         __syncthreads();        // this chunk's rows are there, and everyone is done with the other buffer
         if (r0 + DR_ROWS < n) fetch(r0 + DR_ROWS, dr_smem + (turn ^ 1) * DR_ROWS * ROWF);
         float *orow = a.out + (size_t)(first + r0) * a.heads * a.dv + (size_t)h * a.dv + col;
-        for (int r = 0; r < nr; ++r) {
+        int r = 0;
+        for (; r + 1 < nr; r += 2) {        // two rows a round
+            const float *row1 = buf + r * ROWF, *row2 = row1 + ROWF;
+            const float4 n1 = *reinterpret_cast<const float4 *>(row1 + 2 * KP + DR_COLS);       // g, beta, k . q
+            const float4 n2 = *reinterpret_cast<const float4 *>(row2 + 2 * KP + DR_COLS);
+            const float4 x2 = *reinterpret_cast<const float4 *>(row2 + 2 * KP + DR_COLS + 4);   // k1 . k2, k1 . q2
+            const float v1 = live ? row1[2 * KP + cl] : 0.f, v2 = live ? row2[2 * KP + cl] : 0.f;
+            float k1[NPER], k2[NPER];
+            float a1 = 0.f, b1 = 0.f, a2 = 0.f, b2 = 0.f;
+#pragma unroll
+            for (int j = 0; j < NPER; j += 4) {
+                const float4 ka = *reinterpret_cast<const float4 *>(row1 + part * LP + j), qa = *reinterpret_cast<const float4 *>(row1 + KP + part * LP + j);
+                const float4 kb = *reinterpret_cast<const float4 *>(row2 + part * LP + j), qb = *reinterpret_cast<const float4 *>(row2 + KP + part * LP + j);
+                k1[j] = ka.x; k1[j + 1] = ka.y; k1[j + 2] = ka.z; k1[j + 3] = ka.w;
+                k2[j] = kb.x; k2[j + 1] = kb.y; k2[j + 2] = kb.z; k2[j + 3] = kb.w;
+                a1 = fmaf(s[j], ka.x, a1); a1 = fmaf(s[j + 1], ka.y, a1); a1 = fmaf(s[j + 2], ka.z, a1); a1 = fmaf(s[j + 3], ka.w, a1);
+                b1 = fmaf(s[j], qa.x, b1); b1 = fmaf(s[j + 1], qa.y, b1); b1 = fmaf(s[j + 2], qa.z, b1); b1 = fmaf(s[j + 3], qa.w, b1);
+                a2 = fmaf(s[j], kb.x, a2); a2 = fmaf(s[j + 1], kb.y, a2); a2 = fmaf(s[j + 2], kb.z, a2); a2 = fmaf(s[j + 3], kb.w, a2);
+                b2 = fmaf(s[j], qb.x, b2); b2 = fmaf(s[j + 1], qb.y, b2); b2 = fmaf(s[j + 2], qb.z, b2); b2 = fmaf(s[j + 3], qb.w, b2);
+            }
+#pragma unroll
+            for (int o = 1; o < DR_LANES; o <<= 1) {
+                a1 += __shfl_xor_sync(0xffffffffu, a1, o); b1 += __shfl_xor_sync(0xffffffffu, b1, o);
+                a2 += __shfl_xor_sync(0xffffffffu, a2, o); b2 += __shfl_xor_sync(0xffffffffu, b2, o);
+            }
+            const float w1 = n1.y * (v1 - n1.x * a1);
+            const float o1 = fmaf(w1, n1.z, n1.x * b1);
+            a2 = fmaf(w1, x2.x, n1.x * a2);         // against the state after the first row
+            b2 = fmaf(w1, x2.y, n1.x * b2);
+            const float w2 = n2.y * (v2 - n2.x * a2);
+            const float o2 = fmaf(w2, n2.z, n2.x * b2);
+            const float c0 = n2.x * n1.x, c1 = n2.x * w1;
+#pragma unroll
+            for (int j = 0; j < NPER; ++j) s[j] = fmaf(k2[j], w2, fmaf(k1[j], c1, c0 * s[j]));
+            if (part == 0 && live) {
+                orow[(size_t)r * a.heads * a.dv] = o1;
+                orow[(size_t)(r + 1) * a.heads * a.dv] = o2;
+            }
+        }
+        for (; r < nr; ++r) {               // a chunk's last row where it has an odd number
             const float *rowp = buf + r * ROWF;
             const float4 row = *reinterpret_cast<const float4 *>(rowp + 2 * KP + DR_COLS);      // g, beta, k . q
             const float v = live ? rowp[2 * KP + cl] : 0.f;
@@ -1376,7 +1425,7 @@ JK_EXPORT int jk_delta_rule(const float *c, int ld_c, int q_off, int k_off, int 
     const dim3 grid(heads, nreq, (dv + DR_COLS - 1) / DR_COLS);
 #define LAUNCH(NPER)                                                                                                                         \
     do {                                                                                                                                     \
-        const size_t smem = (size_t)2 * DR_ROWS * (2 * DR_LANES * (NPER + 4) + DR_COLS + 4) * sizeof(float);                                 \
+        const size_t smem = (size_t)2 * DR_ROWS * (2 * DR_LANES * (NPER + 4) + DR_COLS + 8) * sizeof(float);                                 \
         if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<NPER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
         jk_launch(delta_scan_kernel<NPER>, grid, dim3(DR_THREADS), smem, stream, a);                                                         \
     } while (0)

@@ -952,7 +952,7 @@ JK_EXPORT int jk_runner_slot_bytes(const RunnerEnv *env, const RunnerOp *ops, in
                 const long long width = (long long)op.heads * op.v_head_dim;
                 const long long per = (op.head_dim + 7) / 8, nper = per <= 4 ? 4 : (per <= 8 ? 8 : (per <= 16 ? 16 : 32));
                 need(op.in_slot, 4 * rows * op.ld); need(SLOT_TMP, 4 * rows * op.r_off);
-                need(SLOT_SCAN, 4 * ((rows * width + 3) / 4 * 4 + rows * (op.groups * 2 * 8 * nper + 4LL * op.heads)));
+                need(SLOT_SCAN, 4 * ((rows * width + 3) / 4 * 4 + rows * (op.groups * 2 * 8 * nper + 8LL * op.heads)));
                 need(op.out_slot, e * rows * width);
                 break;
             }
